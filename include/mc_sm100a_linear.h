@@ -1,0 +1,250 @@
+/* mc_sm100a_linear.h -- C ABI of the B200 (sm_100a) decode linear-layer library.
+ *
+ * This is the drop-in boundary for ONE path of the reference runtime: the
+ * decode-time linear layers (M=1 GEMV in bf16 and in e4m3 weight-only with a
+ * per-output-row fp32 scale, the fused variants around them, and the M<=64
+ * batched-decode skinny GEMM).  Every entry point below replaces one internal
+ * launcher / engine method of the reference; the citation beside each one is
+ * the reference interface it stands in for (path relative to the reference
+ * project root).  Argument order, meaning and error behaviour follow the
+ * reference; shape restrictions of the reference (hidden size fixed at 2048,
+ * M capped at 8, ...) are lifted.
+ *
+ * Conventions (same as native/include/minicpm_runtime.h:1-12 and
+ * native/kernels/sm120/kernels.h:3-11):
+ *   - extern "C", fixed-width integers, plain pointers; no CUDA or C++ types
+ *     in signatures.  `stream` is a cudaStream_t passed as void* (NULL = the
+ *     legacy default stream).  bf16 travels as raw uint16_t bit patterns,
+ *     e4m3 as uint8_t codes.
+ *   - every pointer named d_* is DEVICE memory; h_* is HOST memory.
+ *   - every call returns mc_status_t; on failure an English message is left
+ *     in a thread-local buffer readable through mc_last_error().
+ *   - no call allocates device memory, synchronises, or takes a host-side
+ *     decision that depends on device data unless its comment says so: the
+ *     launch shapes depend only on the arguments, so a sequence of calls can
+ *     be captured into a CUDA graph and replayed.
+ *   - `pdl` != 0 launches with programmatic stream serialisation; the kernels
+ *     then issue their weight loads before griddepcontrol.wait and release
+ *     their dependents at entry, like the reference kernels do
+ *     (native/kernels/sm120/kernels.h:25-57).
+ *   - there is no CPU and no library-GEMM fallback behind any of these.
+ */
+#ifndef MC_SM100A_LINEAR_H
+#define MC_SM100A_LINEAR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Only the entry points below are exported from the shared library (hidden
+ * visibility otherwise, as native/runtime/export.h does for MC_API). */
+#if defined(__GNUC__)
+#define MC_SM100_API __attribute__((visibility("default")))
+#else
+#define MC_SM100_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: numerically identical to native/include/minicpm_runtime.h:34-44. */
+#ifndef MC_STATUS_T_DEFINED
+#define MC_STATUS_T_DEFINED
+typedef enum mc_status_t {
+    MC_OK = 0,
+    MC_E_INVALID_ARGUMENT = 1,
+    MC_E_IO = 2,
+    MC_E_CUDA = 3,
+    MC_E_MODEL_MISMATCH = 4,
+    MC_E_OUT_OF_MEMORY = 5,
+    MC_E_GRAPH = 6,
+    MC_E_UNSUPPORTED = 7,
+    MC_E_INTERNAL = 100
+} mc_status_t;
+#endif
+
+/* GEMV tactics: values of native/kernels/sm120/kernels.h:109-117.  Tactic 0
+ * (library GEMM) does not exist here and is rejected. */
+#define MC_GEMV_TACTIC_ROWS   1
+#define MC_GEMV_TACTIC_SPLITK 2
+#define MC_GEMV_TACTIC_FP8    3
+
+/* Thread-local diagnostic of the last failing call on this thread
+ * (native/include/minicpm_runtime.h:131; native/runtime/error.cpp:14-41). */
+MC_SM100_API const char* mc_sm100_last_error(void);
+
+/* Library / device probe.  Fills sm_count, L2 bytes and compute capability of
+ * the CURRENT device; MC_E_UNSUPPORTED unless it is compute capability 10.x
+ * (stands where the reference checks for 12.0, native/runtime/model.cpp:133-139). */
+MC_SM100_API mc_status_t mc_sm100_device_check(int32_t* out_sm_count, uint64_t* out_l2_bytes,
+                                  int32_t* out_cc_major, int32_t* out_cc_minor);
+
+/* ---------------------------------------------------------------- M = 1 ---- */
+
+/* y[N] = bf16( W[N,K] . x[K] ), fp32 accumulate, one rounding.
+ * Replaces launch_decode_gemv (native/kernels/sm120/kernels.h:666-672,
+ * native/kernels/sm120/gemv.cu:382-431).  W row-major, 16-byte aligned,
+ * K % 8 == 0.  tactic ROWS: one pass.  tactic SPLITK: K is cut into split_s
+ * equal segments ((K/split_s) % 8 == 0), fp32 partials [split_s, N] go to
+ * d_split_partial and are merged in fixed order (no atomics: bit-reproducible). */
+MC_SM100_API mc_status_t mc_sm100_decode_gemv(const uint16_t* d_w, const uint16_t* d_x, uint16_t* d_y,
+                                 uint32_t N, uint32_t K, int32_t tactic, uint32_t split_s,
+                                 float* d_split_partial, void* stream, int32_t pdl);
+
+/* y[N] = bf16( scale[n] * sum_k e4m3(W[n,k]) * x[k] ); the row scale multiplies
+ * the finished fp32 sum once.  Replaces launch_gemv_fp8
+ * (native/kernels/sm120/kernels.h:721-726, gemv_fp8.cu:694-721).  Any K; the
+ * vector path needs K % 16 == 0 and 16-byte aligned W and x, everything else
+ * takes a byte-wise path with the same arithmetic.  Codes 0x7F/0xFF decode to
+ * +/-480 like the reference's bit decoder (kernels.h:120-125). */
+MC_SM100_API mc_status_t mc_sm100_gemv_fp8(const uint8_t* d_w, const float* d_scale, const uint16_t* d_x,
+                              uint16_t* d_y, uint32_t N, uint32_t K, void* stream, int32_t pdl);
+
+/* Fused prologue: res_out = bf16(res_in + addend) (addend may be NULL: plain
+ * copy), h = rmsnorm(res_out) * norm_w, y = W . h.  The normalised vector
+ * stays on chip.  Replace launch_gemv_rows_prologue / launch_gemv_fp8_prologue
+ * (native/kernels/sm120/kernels.h:735-748, gemv.cu:148-246, gemv_fp8.cu:213-315);
+ * `n` (= K of the GEMV) is no longer fixed at 2048.  res_in/res_out must be
+ * different buffers (the reference ping-pongs them, forward.cpp:206-237). */
+MC_SM100_API mc_status_t mc_sm100_gemv_rows_prologue(const uint16_t* d_w, const uint16_t* d_res_in,
+                                        const uint16_t* d_addend, const uint16_t* d_norm_w,
+                                        uint16_t* d_res_out, uint16_t* d_y, uint32_t N,
+                                        uint32_t n, float eps, void* stream, int32_t pdl);
+MC_SM100_API mc_status_t mc_sm100_gemv_fp8_prologue(const uint8_t* d_w, const float* d_scale,
+                                       const uint16_t* d_res_in, const uint16_t* d_addend,
+                                       const uint16_t* d_norm_w, uint16_t* d_res_out,
+                                       uint16_t* d_y, uint32_t N, uint32_t n, float eps,
+                                       void* stream, int32_t pdl);
+
+/* Down projection with the SwiGLU computed on the way in:
+ * h[k] = bf16( silu(gate_up[k]) * gate_up[K+k] ), y = W[N,K] . h.
+ * Replace launch_gemv_rows_swiglu / launch_gemv_fp8_swiglu
+ * (native/kernels/sm120/kernels.h:753-764); K is no longer fixed at 6144. */
+MC_SM100_API mc_status_t mc_sm100_gemv_rows_swiglu(const uint16_t* d_w, const uint16_t* d_gate_up,
+                                      uint16_t* d_y, uint32_t N, uint32_t K, void* stream,
+                                      int32_t pdl);
+MC_SM100_API mc_status_t mc_sm100_gemv_fp8_swiglu(const uint8_t* d_w, const float* d_scale,
+                                     const uint16_t* d_gate_up, uint16_t* d_y, uint32_t N,
+                                     uint32_t K, void* stream, int32_t pdl);
+
+/* Fused gate_up projection with a SwiGLU EPILOGUE (the B200 arena layout):
+ * the weight holds gate and up rows interleaved (row 2j = gate_j, row 2j+1 =
+ * up_j; see mc_sm100_interleave_rows), N = 2*I rows in total, and
+ * y[m, j] = bf16( silu(bf16 g) * bf16 u ) with g/u the bf16-ROUNDED dot
+ * products -- bit-compatible with running the plain GEMV and then
+ * swiglu_gated_kernel (native/kernels/sm120/swiglu.cu:57-70;
+ * tools/reference_forward.py:293-294).  d_scale == NULL selects bf16 weights
+ * (d_w read as uint16_t), otherwise e4m3 weights with interleaved row scales.
+ * M in [1,4]; x [M,K], y [M, N/2]. */
+MC_SM100_API mc_status_t mc_sm100_gate_up_swiglu(const void* d_w_interleaved, const float* d_scale_interleaved,
+                                    const uint16_t* d_x, uint16_t* d_y, uint32_t M, uint32_t N,
+                                    uint32_t K, void* stream, int32_t pdl);
+
+/* Arena re-layout helper for the call above: dst row 2j = src row j, dst row
+ * 2j+1 = src row I+j, for rows of row_bytes bytes (weights) -- call it again
+ * with row_bytes = 4 for the fp32 scales.  Runs on the device, src != dst. */
+MC_SM100_API mc_status_t mc_sm100_interleave_rows(const void* d_src, void* d_dst, uint32_t I,
+                                     uint32_t row_bytes, void* stream);
+
+/* ------------------------------------------------------------ 2 <= M <= 64 -- */
+
+/* y[M,N] = bf16( scale[n] * sum_k e4m3(W[n,k]) * x[m,k] ), weight-only fp8.
+ * Replaces launch_gemv_fp8_rows_m (native/kernels/sm120/kernels.h:774-779),
+ * whose cap of M <= 8 becomes M <= 64.  M <= 4 runs on CUDA cores and every
+ * output row is bit-equal to the M=1 call on that row; larger M dequantises
+ * e4m3 -> bf16 (exact) on the way into shared memory and uses tcgen05 MMA. */
+MC_SM100_API mc_status_t mc_sm100_gemv_fp8_rows_m(const uint8_t* d_w, const float* d_scale,
+                                     const uint16_t* d_x, uint16_t* d_y, uint32_t M,
+                                     uint32_t N, uint32_t K, void* stream, int32_t pdl);
+
+/* C[M,N] = bf16( B[M,K] . A[N,K]^T ): d_a is the WEIGHT [N,K], d_b the
+ * activation [M,K], both row-major (operand order of GemmEngine::gemm_bf16,
+ * native/runtime/gemm.h:3-11, 61-63; native/runtime/gemm.cpp:316-380).
+ * M in [1,64].  workspace: fp32 split-K partials, at least
+ * mc_sm100_gemm_workspace_bytes(M,N,K) bytes (the reference passes its 16 MB
+ * per-session workspace here); may be NULL when that function returns 0. */
+MC_SM100_API mc_status_t mc_sm100_gemm_bf16(void* stream, void* d_workspace, size_t ws_size, uint32_t M,
+                               uint32_t N, uint32_t K, const void* d_a, const void* d_b,
+                               void* d_c);
+MC_SM100_API size_t mc_sm100_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K);
+
+/* W8A8 form of the batched GEMM (GemmEngine::gemm_fp8_q / gemm_fp8,
+ * native/runtime/gemm.h:64-90): Y = (Wq*w_scale[n]) . (Xq*x_scale[m])^T with
+ * tcgen05 kind::f8f6f4.  gemm_fp8 quantises the bf16 activation per row first
+ * (launch_quant_rows, native/kernels/sm120/quant.cu:98-136) into the caller's
+ * scratch.  This is NOT the weight-only arithmetic: it is judged against the
+ * quantisation-aware CPU statement. */
+MC_SM100_API mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size, uint32_t M,
+                                uint32_t N, uint32_t K, const void* d_w_fp8,
+                                const float* d_w_scale, const void* d_x_fp8,
+                                const float* d_x_scale, uint16_t* d_y_bf16);
+MC_SM100_API mc_status_t mc_sm100_gemm_fp8(void* stream, void* d_workspace, size_t ws_size, uint32_t M,
+                              uint32_t N, uint32_t K, const void* d_w_fp8, const float* d_w_scale,
+                              const uint16_t* d_x_bf16, uint16_t* d_y_bf16,
+                              void* d_x_fp8_scratch, float* d_x_scale_scratch);
+
+/* bf16 [M,K] -> e4m3 [M,K] + scale[M] (amax/448; all-zero row -> scale 1), and
+ * y[m,n] *= w_scale[n]*x_scale[m] (x_scale may be NULL).  Replace
+ * launch_quant_rows / launch_post_scale_rows (kernels.h:785-798). */
+MC_SM100_API mc_status_t mc_sm100_quant_rows(const uint16_t* d_x, uint8_t* d_xq, float* d_scale, uint32_t M,
+                                uint32_t K, void* stream);
+MC_SM100_API mc_status_t mc_sm100_post_scale_rows(uint16_t* d_y, const float* d_w_scale,
+                                     const float* d_x_scale, uint32_t M, uint32_t N,
+                                     void* stream);
+
+/* ------------------------------------------------------- lm_head / greedy --- */
+
+/* Greedy argmax over bf16 logits compared as fp32, ties to the lowest index,
+ * rows [n_rows, vocab]; writes one int32 per row.  Two-stage; d_stage needs
+ * mc_sm100_argmax_stage_bytes(n_rows) bytes.  Replaces
+ * launch_sampling_greedy_bf16 / launch_batch_argmax_bf16
+ * (native/kernels/sm120/sampling.cu:637-685, 186-234).  index_base is added
+ * to the indices (vocab shards); d_out_val (optional) receives the winning
+ * value as fp32 so that shards can be compared across ranks. */
+MC_SM100_API mc_status_t mc_sm100_argmax_bf16(const uint16_t* d_logits, uint32_t n_rows, uint32_t vocab,
+                                 uint32_t row_stride, int32_t index_base, void* d_stage,
+                                 int32_t* d_out_idx, float* d_out_val, void* stream,
+                                 int32_t pdl);
+MC_SM100_API size_t mc_sm100_argmax_stage_bytes(uint32_t n_rows);
+
+/* lm_head GEMV (bf16 weights when d_scale == NULL, else e4m3 + row scales) for
+ * M in [1,8] rows with the per-shard argmax fused behind it: logits [M,N] are
+ * written (row stride y_stride elements) and (value, index_base + index) of
+ * each row's maximum go to d_out_val / d_out_idx.  N need not be a multiple
+ * of anything (vocab 122753).  Stands for the reference's lm_head GEMV +
+ * two-stage argmax pair (native/runtime/forward.cpp:443-489). */
+MC_SM100_API mc_status_t mc_sm100_lm_head_argmax(const void* d_w, const float* d_scale, const uint16_t* d_x,
+                                    uint16_t* d_logits, uint32_t y_stride, uint32_t M,
+                                    uint32_t N, uint32_t K, int32_t index_base, void* d_stage,
+                                    int32_t* d_out_idx, float* d_out_val, void* stream,
+                                    int32_t pdl);
+
+/* ------------------------------------------------- host-buffer convenience -- */
+
+/* One linear call with HOST activations: copies h_x [M,K] to the device,
+ * runs the matching kernel above on weights already resident in device
+ * memory, copies y back and synchronises the stream.  kind: 0 plain linear,
+ * 1 gate_up + SwiGLU epilogue (interleaved weights).  d_scale NULL = bf16
+ * weights.  d_x_stage / d_y_stage are caller-provided device staging buffers
+ * (M*K and M*N bf16), d_workspace as for mc_sm100_gemm_bf16.  This is the
+ * call the end-to-end benchmark times; it mirrors what mc_decode_one does
+ * around a step (H2D of the step input, D2H of the result, one sync;
+ * native/runtime/decode_executor.cpp:163-289). */
+MC_SM100_API mc_status_t mc_sm100_linear_host(int32_t kind, const void* d_w, const float* d_scale,
+                                 const uint16_t* h_x, uint16_t* h_y, uint32_t M, uint32_t N,
+                                 uint32_t K, uint16_t* d_x_stage, uint16_t* d_y_stage,
+                                 void* d_workspace, size_t ws_size, void* stream);
+
+/* ---------------------------------------------------------------- debug hook -- */
+
+/* Not part of the frozen surface (same standing as the reference's
+ * mc_debug_* exports, native/runtime/session.cpp:631-723): selects the
+ * arithmetic form of the streaming kernels per weight type for A/B runs.
+ * 0 = widen to fp32 then FFMA, 1 = mixed-precision FMA on bf16 operands;
+ * any other value keeps the current form.  Both forms give identical bits. */
+MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MC_SM100A_LINEAR_H */

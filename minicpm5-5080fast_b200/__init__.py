@@ -1,0 +1,202 @@
+"""ctypes view of libmc_sm100a_linear.so -- the B200 decode linear-layer library.
+
+The product is the C-ABI shared library (`include/mc_sm100a_linear.h`); this
+module only loads it and gives tests and the benchmark functions with the
+reference launchers' names and argument order
+(native/kernels/sm120/kernels.h:657-798, native/runtime/gemm.h:39-90).
+PyTorch tensors are used purely as device-memory handles (`data_ptr()`); there
+is no PyTorch, Triton or CPU implementation behind any call: if the library is
+missing or a call fails, an exception is raised.
+
+The directory name contains a hyphen, so import it with
+`importlib.import_module("minicpm5-5080fast_b200")`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmc_sm100a_linear.so")
+
+MC_OK = 0
+MC_E_INVALID_ARGUMENT = 1
+MC_E_CUDA = 3
+MC_E_UNSUPPORTED = 7
+TACTIC_ROWS, TACTIC_SPLITK, TACTIC_FP8 = 1, 2, 3
+
+_u16p = C.c_void_p
+_vp = C.c_void_p
+_u32 = C.c_uint32
+_i32 = C.c_int32
+
+# name -> (restype, argtypes): mirrors include/mc_sm100a_linear.h one to one
+SIGNATURES = {
+    "mc_sm100_last_error": (C.c_char_p, []),
+    "mc_sm100_device_check": (_i32, [C.POINTER(_i32), C.POINTER(C.c_uint64), C.POINTER(_i32), C.POINTER(_i32)]),
+    "mc_sm100_decode_gemv": (_i32, [_vp, _vp, _vp, _u32, _u32, _i32, _u32, _vp, _vp, _i32]),
+    "mc_sm100_gemv_fp8": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _i32]),
+    "mc_sm100_gemv_rows_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
+    "mc_sm100_gemv_fp8_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
+    "mc_sm100_gemv_rows_swiglu": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp, _i32]),
+    "mc_sm100_gemv_fp8_swiglu": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _i32]),
+    "mc_sm100_gate_up_swiglu": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _i32]),
+    "mc_sm100_interleave_rows": (_i32, [_vp, _vp, _u32, _u32, _vp]),
+    "mc_sm100_gemv_fp8_rows_m": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _i32]),
+    "mc_sm100_gemm_bf16": (_i32, [_vp, _vp, C.c_size_t, _u32, _u32, _u32, _vp, _vp, _vp]),
+    "mc_sm100_gemm_workspace_bytes": (C.c_size_t, [_u32, _u32, _u32]),
+    "mc_sm100_gemm_fp8_q": (_i32, [_vp, _vp, C.c_size_t, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "mc_sm100_gemm_fp8": (_i32, [_vp, _vp, C.c_size_t, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mc_sm100_quant_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mc_sm100_post_scale_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mc_sm100_argmax_bf16": (_i32, [_vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_argmax_stage_bytes": (C.c_size_t, [_u32]),
+    "mc_sm100_lm_head_argmax": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_linear_host": (_i32, [_i32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "mc_sm100_debug_set_math": (None, [_i32, _i32]),
+}
+
+
+class McError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"mc_status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python minicpm5-5080fast_b200/build.py`; "
+                "there is no fallback implementation")
+        h = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = h
+    return _lib
+
+
+def last_error() -> str:
+    return (lib().mc_sm100_last_error() or b"").decode()
+
+
+def _check(status: int) -> None:
+    if status != MC_OK:
+        raise McError(status, last_error())
+
+
+def _p(t) -> int | None:
+    """Device (or pinned host) address of a tensor, None passes NULL."""
+    return None if t is None else t.data_ptr()
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    s = stream if isinstance(stream, int) else stream.cuda_stream
+    return s or None
+
+
+# ---- launchers, named after the reference's ------------------------------------------
+def device_check():
+    sm, l2, mj, mn = _i32(), C.c_uint64(), _i32(), _i32()
+    _check(lib().mc_sm100_device_check(C.byref(sm), C.byref(l2), C.byref(mj), C.byref(mn)))
+    return {"sm_count": sm.value, "l2_bytes": l2.value, "cc": (mj.value, mn.value)}
+
+
+def launch_decode_gemv(w, x, y, N, K, tactic=TACTIC_ROWS, split_s=0, split_partial=None, stream=None, pdl=False):
+    _check(lib().mc_sm100_decode_gemv(_p(w), _p(x), _p(y), N, K, tactic, split_s, _p(split_partial),
+                                      _stream(stream), int(pdl)))
+
+
+def launch_gemv_fp8(w, scale, x, y, N, K, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_fp8(_p(w), _p(scale), _p(x), _p(y), N, K, _stream(stream), int(pdl)))
+
+
+def launch_gemv_rows_prologue(w, res_in, addend, norm_w, res_out, y, N, n, eps, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_rows_prologue(_p(w), _p(res_in), _p(addend), _p(norm_w), _p(res_out), _p(y),
+                                             N, n, eps, _stream(stream), int(pdl)))
+
+
+def launch_gemv_fp8_prologue(w, scale, res_in, addend, norm_w, res_out, y, N, n, eps, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_fp8_prologue(_p(w), _p(scale), _p(res_in), _p(addend), _p(norm_w), _p(res_out),
+                                            _p(y), N, n, eps, _stream(stream), int(pdl)))
+
+
+def launch_gemv_rows_swiglu(w, gate_up, y, N, K, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_rows_swiglu(_p(w), _p(gate_up), _p(y), N, K, _stream(stream), int(pdl)))
+
+
+def launch_gemv_fp8_swiglu(w, scale, gate_up, y, N, K, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_fp8_swiglu(_p(w), _p(scale), _p(gate_up), _p(y), N, K, _stream(stream), int(pdl)))
+
+
+def launch_gate_up_swiglu(w_il, scale_il, x, y, M, N, K, stream=None, pdl=False):
+    _check(lib().mc_sm100_gate_up_swiglu(_p(w_il), _p(scale_il), _p(x), _p(y), M, N, K, _stream(stream), int(pdl)))
+
+
+def interleave_rows(src, dst, I, row_bytes, stream=None):
+    _check(lib().mc_sm100_interleave_rows(_p(src), _p(dst), I, row_bytes, _stream(stream)))
+
+
+def launch_gemv_fp8_rows_m(w, scale, x, y, M, N, K, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_fp8_rows_m(_p(w), _p(scale), _p(x), _p(y), M, N, K, _stream(stream), int(pdl)))
+
+
+def gemm_workspace_bytes(M, N, K) -> int:
+    return lib().mc_sm100_gemm_workspace_bytes(M, N, K)
+
+
+def gemm_bf16(stream, workspace, ws_size, M, N, K, a_weight, b_act, c):
+    _check(lib().mc_sm100_gemm_bf16(_stream(stream), _p(workspace), ws_size, M, N, K, _p(a_weight), _p(b_act), _p(c)))
+
+
+def gemm_fp8_q(stream, workspace, ws_size, M, N, K, w_fp8, w_scale, x_fp8, x_scale, y):
+    _check(lib().mc_sm100_gemm_fp8_q(_stream(stream), _p(workspace), ws_size, M, N, K, _p(w_fp8), _p(w_scale),
+                                     _p(x_fp8), _p(x_scale), _p(y)))
+
+
+def gemm_fp8(stream, workspace, ws_size, M, N, K, w_fp8, w_scale, x_bf16, y, x_fp8_scratch, x_scale_scratch):
+    _check(lib().mc_sm100_gemm_fp8(_stream(stream), _p(workspace), ws_size, M, N, K, _p(w_fp8), _p(w_scale),
+                                   _p(x_bf16), _p(y), _p(x_fp8_scratch), _p(x_scale_scratch)))
+
+
+def launch_quant_rows(x, xq, scale, M, K, stream=None):
+    _check(lib().mc_sm100_quant_rows(_p(x), _p(xq), _p(scale), M, K, _stream(stream)))
+
+
+def launch_post_scale_rows(y, w_scale, x_scale, M, N, stream=None):
+    _check(lib().mc_sm100_post_scale_rows(_p(y), _p(w_scale), _p(x_scale), M, N, _stream(stream)))
+
+
+def argmax_stage_bytes(n_rows) -> int:
+    return lib().mc_sm100_argmax_stage_bytes(n_rows)
+
+
+def launch_argmax_bf16(logits, n_rows, vocab, row_stride, index_base, stage, out_idx, out_val=None,
+                       stream=None, pdl=False):
+    _check(lib().mc_sm100_argmax_bf16(_p(logits), n_rows, vocab, row_stride, index_base, _p(stage), _p(out_idx),
+                                      _p(out_val), _stream(stream), int(pdl)))
+
+
+def launch_lm_head_argmax(w, scale, x, logits, y_stride, M, N, K, index_base, stage, out_idx, out_val=None,
+                          stream=None, pdl=False):
+    _check(lib().mc_sm100_lm_head_argmax(_p(w), _p(scale), _p(x), _p(logits), y_stride, M, N, K, index_base,
+                                         _p(stage), _p(out_idx), _p(out_val), _stream(stream), int(pdl)))
+
+
+def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=None, ws_size=0, stream=None):
+    _check(lib().mc_sm100_linear_host(kind, _p(w), _p(scale), _p(h_x), _p(h_y), M, N, K, _p(x_stage),
+                                      _p(y_stage), _p(workspace), ws_size, _stream(stream)))
+
+
+def debug_set_math(bf16_math=-1, fp8_math=-1):
+    lib().mc_sm100_debug_set_math(bf16_math, fp8_math)

@@ -1,0 +1,136 @@
+// common.cuh -- shared device/host helpers of the sm_100a decode linear-layer library.
+#pragma once
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include <cuda_runtime.h>
+
+#include "mc_sm100a_linear.h"
+
+namespace mcl {
+
+// ---- thread-local diagnostics (role of native/runtime/error.cpp:14-41) ----
+void set_error(const char* fmt, ...);
+void clear_error();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0u; }
+
+// Number of SMs of the current device, cached per device id (no allocation,
+// no synchronisation; cudaDeviceGetAttribute is a host-side query).
+int sm_count();
+
+// Launch with or without the programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+#define MCL_CHECK_LAUNCH(what)                                                   \
+    do {                                                                         \
+        const cudaError_t e__ = cudaGetLastError();                              \
+        if (e__ != cudaSuccess) {                                                \
+            mcl::set_error("%s launch failed: %s", what, cudaGetErrorString(e__)); \
+            return MC_E_CUDA;                                                    \
+        }                                                                        \
+    } while (0)
+
+#if defined(__CUDACC__)
+
+// ---- programmatic dependent launch ----
+// wait: block until the producer grid's memory is visible (no-op when the
+// kernel was not launched with the attribute).  trigger: let the dependent
+// grid start its own prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+// ---- streaming loads: read-only path, do not keep the line in L1 ----
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// ---- bf16 helpers on raw bits ----
+__device__ __forceinline__ float bf16lo(uint32_t p) { return __uint_as_float(p << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
+
+// round-to-nearest-even narrowing, NaN kept quiet (same result as
+// __float2bfloat16_rn for every finite input and infinities).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+    uint32_t u = __float_as_uint(f);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+// fp32 fused multiply-add taking two bf16 operands directly (sm_100 mixed
+// precision form): acc = a*b + acc with the exact product, one rounding.
+__device__ __forceinline__ void fma_bf16(float& acc, uint16_t a, uint16_t b) {
+    asm("fma.rn.f32.bf16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
+}
+
+// ---- e4m3 ----
+// Two e4m3 codes (bytes `lo`/`hi` selected by the PRMT selector) -> packed
+// bf16x2 holding value * 2^-120 each: the 7 magnitude bits dropped at bit 4 of
+// a bf16 are exponent(4)+mantissa(3) with the exponent biased by 7 instead of
+// 127.  Exact for normals and subnormals; codes 0x7F/0xFF come out as 480 like
+// the reference's bit decoder.
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2_scaled(uint32_t w) {
+    uint32_t t;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(t) : "r"(w), "n"(SEL));  // bytes -> [b_hi,0,b_lo,0]
+    return (t & 0x80008000u) | ((t >> 4) & 0x07F007F0u);
+}
+// 2^120, the factor that undoes the scaling above (applied to the finished sum).
+#define MCL_E4M3_UNSCALE 1.329227995784916e36f
+
+// Hardware conversion e4m3x2 -> f16x2 (exact), then f16 -> f32 (exact).
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint16_t pair) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(pair));
+    float2 r;
+    asm("{.reg .f16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi;}"
+        : "=f"(r.x), "=f"(r.y)
+        : "r"(h2));
+    return r;
+}
+
+// byte-wise decode with the reference's bit construction
+// (native/kernels/sm120/kernels.h:131-148), restated.
+__device__ __forceinline__ float e4m3_to_f32(uint32_t c) {
+    const uint32_t sign = (c & 0x80u) << 24;
+    const uint32_t mag = c & 0x7Fu;
+    // value*2^-120 as fp32 bits, then exact rescale by 2^120 (subnormals of the
+    // small format are fp32 subnormals here; the product is exact).
+    return __uint_as_float(sign | (mag << 20)) * MCL_E4M3_UNSCALE;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    return v;
+}
+
+// silu(g)*u with the reference's formula g/(1+expf(-g)) (swiglu.cu:66-69).
+__device__ __forceinline__ float swiglu_f32(float g, float u) {
+    return (g / (1.0f + expf(-g))) * u;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace mcl
