@@ -140,6 +140,15 @@ MC_SM100_API mc_status_t mc_sm100_gate_up_swiglu(const void* d_w_interleaved, co
                                     const uint16_t* d_x, uint16_t* d_y, uint32_t M, uint32_t N,
                                     uint32_t K, void* stream, int32_t pdl);
 
+/* The same with the residual-add + RMSNorm prologue in front (M = 1): what the
+ * reference does for gate_up with launch_gemv_*_prologue followed by the
+ * SwiGLU of the down projection (native/runtime/forward.cpp:306-373), in one
+ * kernel on the interleaved layout.  y [N/2]. */
+MC_SM100_API mc_status_t mc_sm100_gate_up_swiglu_prologue(
+    const void* d_w_interleaved, const float* d_scale_interleaved, const uint16_t* d_res_in,
+    const uint16_t* d_addend, const uint16_t* d_norm_w, uint16_t* d_res_out, uint16_t* d_y,
+    uint32_t N, uint32_t n, float eps, void* stream, int32_t pdl);
+
 /* Arena re-layout helper for the call above: dst row 2j = src row j, dst row
  * 2j+1 = src row I+j, for rows of row_bytes bytes (weights) -- call it again
  * with row_bytes = 4 for the fp32 scales.  Runs on the device, src != dst. */
@@ -218,6 +227,15 @@ MC_SM100_API mc_status_t mc_sm100_lm_head_argmax(const void* d_w, const float* d
                                     uint32_t N, uint32_t K, int32_t index_base, void* d_stage,
                                     int32_t* d_out_idx, float* d_out_val, void* stream,
                                     int32_t pdl);
+
+/* The same for M = 1 with the final residual-add + RMSNorm in front (the
+ * reference runs lm_head through launch_gemv_fp8_prologue,
+ * native/runtime/forward.cpp:443-462). */
+MC_SM100_API mc_status_t mc_sm100_lm_head_argmax_prologue(
+    const void* d_w, const float* d_scale, const uint16_t* d_res_in, const uint16_t* d_addend,
+    const uint16_t* d_norm_w, uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n,
+    float eps, int32_t index_base, void* d_stage, int32_t* d_out_idx, float* d_out_val,
+    void* stream, int32_t pdl);
 
 /* ------------------------------------------------- host-buffer convenience -- */
 

@@ -41,6 +41,7 @@ SIGNATURES = {
     "mc_sm100_gemv_rows_swiglu": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp, _i32]),
     "mc_sm100_gemv_fp8_swiglu": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _i32]),
     "mc_sm100_gate_up_swiglu": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _i32]),
+    "mc_sm100_gate_up_swiglu_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
     "mc_sm100_interleave_rows": (_i32, [_vp, _vp, _u32, _u32, _vp]),
     "mc_sm100_gemv_fp8_rows_m": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _i32]),
     "mc_sm100_gemm_bf16": (_i32, [_vp, _vp, C.c_size_t, _u32, _u32, _u32, _vp, _vp, _vp]),
@@ -52,6 +53,8 @@ SIGNATURES = {
     "mc_sm100_argmax_bf16": (_i32, [_vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_argmax_stage_bytes": (C.c_size_t, [_u32]),
     "mc_sm100_lm_head_argmax": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_lm_head_argmax_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _i32,
+                                                _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_linear_host": (_i32, [_i32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
 }
@@ -143,6 +146,12 @@ def launch_gate_up_swiglu(w_il, scale_il, x, y, M, N, K, stream=None, pdl=False)
     _check(lib().mc_sm100_gate_up_swiglu(_p(w_il), _p(scale_il), _p(x), _p(y), M, N, K, _stream(stream), int(pdl)))
 
 
+def launch_gate_up_swiglu_prologue(w_il, scale_il, res_in, addend, norm_w, res_out, y, N, n, eps,
+                                   stream=None, pdl=False):
+    _check(lib().mc_sm100_gate_up_swiglu_prologue(_p(w_il), _p(scale_il), _p(res_in), _p(addend), _p(norm_w),
+                                                  _p(res_out), _p(y), N, n, eps, _stream(stream), int(pdl)))
+
+
 def interleave_rows(src, dst, I, row_bytes, stream=None):
     _check(lib().mc_sm100_interleave_rows(_p(src), _p(dst), I, row_bytes, _stream(stream)))
 
@@ -191,6 +200,13 @@ def launch_lm_head_argmax(w, scale, x, logits, y_stride, M, N, K, index_base, st
                           stream=None, pdl=False):
     _check(lib().mc_sm100_lm_head_argmax(_p(w), _p(scale), _p(x), _p(logits), y_stride, M, N, K, index_base,
                                          _p(stage), _p(out_idx), _p(out_val), _stream(stream), int(pdl)))
+
+
+def launch_lm_head_argmax_prologue(w, scale, res_in, addend, norm_w, res_out, logits, N, n, eps, index_base,
+                                   stage, out_idx, out_val=None, stream=None, pdl=False):
+    _check(lib().mc_sm100_lm_head_argmax_prologue(_p(w), _p(scale), _p(res_in), _p(addend), _p(norm_w),
+                                                  _p(res_out), _p(logits), N, n, eps, index_base, _p(stage),
+                                                  _p(out_idx), _p(out_val), _stream(stream), int(pdl)))
 
 
 def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=None, ws_size=0, stream=None):

@@ -63,7 +63,8 @@ inline mc_status_t launch_rows_shape(const RowsArgs& a, uint32_t splits, cudaStr
 }
 
 // Entry of one translation unit.  M in [1,4]; supported (PRO, EPI) pairs:
-// M == 1: every prologue with EPI_STORE, PRO_NONE with every epilogue;
+// M == 1: PRO_NONE with every epilogue, PRO_RESNORM with STORE / SWIGLU / ARGMAX,
+// PRO_SWIGLU with STORE;
 // M  > 1: PRO_NONE with STORE / SWIGLU / ARGMAX.
 template <int WB, int MATH>
 mc_status_t launch_rows(int M, int pro, int epi, const RowsArgs& a, uint32_t splits,
@@ -83,6 +84,8 @@ mc_status_t launch_rows(int M, int pro, int epi, const RowsArgs& a, uint32_t spl
         MCL_ROWS_CASE(1, PRO_NONE, EPI_ARGMAX)                                           \
         MCL_ROWS_CASE(1, PRO_NONE, EPI_PARTIAL)                                          \
         MCL_ROWS_CASE(1, PRO_RESNORM, EPI_STORE)                                         \
+        MCL_ROWS_CASE(1, PRO_RESNORM, EPI_SWIGLU)                                        \
+        MCL_ROWS_CASE(1, PRO_RESNORM, EPI_ARGMAX)                                        \
         MCL_ROWS_CASE(1, PRO_SWIGLU, EPI_STORE)                                          \
         MCL_ROWS_CASE(2, PRO_NONE, EPI_STORE)                                            \
         MCL_ROWS_CASE(2, PRO_NONE, EPI_SWIGLU)                                           \

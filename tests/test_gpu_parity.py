@@ -1,0 +1,339 @@
+"""GPU: every entry point of the C ABI against the CPU oracle on seeded inputs,
+against the fixtures generated from the reference, and on the edge cases the
+reference's kernel tests use (native/tests/kernel_ops.cpp:1262-1268, 5380-5393)."""
+import numpy as np
+import pytest
+
+import oracle_np as onp
+from parity import check_close
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+K_B, QKV_B, I_B, V_B = 2304, 3456, 5760, 122753
+
+
+@pytest.fixture(scope="module")
+def g(pkg):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    info = pkg.device_check()
+    assert info["cc"][0] == 10
+    import gpu_util
+    return gpu_util
+
+
+def run_bf16(pkg, g, w, x, tactic=1, split=0, pdl=False):
+    N, K = w.shape
+    dw, dx, dy = g.dev(w), g.dev(x), g.empty_u16(N)
+    part = torch.empty(max(split, 1) * N, dtype=torch.float32, device="cuda") if split else None
+    pkg.launch_decode_gemv(dw, dx, dy, N, K, tactic, split, part, pdl=pdl)
+    g.sync()
+    return g.host_u16(dy)
+
+
+def run_fp8(pkg, g, q, sc, x, pdl=False):
+    N, K = q.shape
+    dq, ds, dx, dy = g.dev(q), g.dev(sc), g.dev(x), g.empty_u16(N)
+    pkg.launch_gemv_fp8(dq, ds, dx, dy, N, K, pdl=pdl)
+    g.sync()
+    return g.host_u16(dy)
+
+
+# ---- M = 1 bf16 ----------------------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(1, 8), (7, 64), (17, 104), (8, 2048), (255, 2304), (2560, 2048), (2048, 6144),
+                                 (1000, 8192), (QKV_B, K_B), (K_B, K_B), (K_B, I_B)])
+@pytest.mark.parametrize("math", [0, 1])
+def test_decode_gemv_rows(pkg, g, N, K, math):
+    pkg.debug_set_math(math, -1)
+    w = onp.seeded_bf16(1000 + N + K, (N, K), 0.02)
+    x = onp.seeded_bf16(2000 + N + K, (K,), 1.0)
+    got = run_bf16(pkg, g, w, x)
+    check_close(got, onp.linear_bf16(w, x), what=f"rows N={N} K={K}")
+    got2 = run_bf16(pkg, g, w, x, pdl=True)
+    assert np.array_equal(got, got2), "PDL launch must give identical bits"
+    pkg.debug_set_math(1, -1)
+
+
+def test_math_forms_bit_identical(pkg, g):
+    w = onp.seeded_bf16(31, (777, 2304), 0.02)
+    x = onp.seeded_bf16(32, (2304,), 1.0)
+    q, sc = onp.make_fp8_weight(w)
+    pkg.debug_set_math(0, 0)
+    a, b = run_bf16(pkg, g, w, x), run_fp8(pkg, g, q, sc, x)
+    pkg.debug_set_math(1, 1)
+    assert np.array_equal(a, run_bf16(pkg, g, w, x))
+    assert np.array_equal(b, run_fp8(pkg, g, q, sc, x))
+
+
+@pytest.mark.parametrize("N,K,S", [(64, 256, 2), (2048, 2048, 8), (K_B, K_B, 4), (K_B, I_B, 8), (QKV_B, K_B, 2)])
+def test_decode_gemv_splitk(pkg, g, N, K, S):
+    w = onp.seeded_bf16(3000 + N + K, (N, K), 0.02)
+    x = onp.seeded_bf16(4000 + N + K, (K,), 1.0)
+    a = run_bf16(pkg, g, w, x, tactic=2, split=S)
+    check_close(a, onp.linear_bf16(w, x), what=f"splitK N={N} K={K} S={S}")
+    assert np.array_equal(a, run_bf16(pkg, g, w, x, tactic=2, split=S)), "split-K must be deterministic"
+
+
+def test_baseline_config1_against_reference_fixture(pkg, g, golden):
+    w = onp.seeded_bf16(onp.SEED_BASE + 1000, (QKV_B, K_B), 0.02)
+    x = onp.seeded_bf16(onp.SEED_BASE + 1001, (K_B,), 1.0)
+    check_close(run_bf16(pkg, g, w, x), golden["baseline"]["c1_y"], what="config1 vs reference output")
+
+
+# ---- M = 1 fp8 -------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(1, 16), (8, 2048), (24, 2048), (255, 2048), (2560, 2048), (2048, 6144),
+                                 (1000, 8192), (64, 100), (33, 2056), (2 * I_B, K_B), (K_B, I_B)])
+@pytest.mark.parametrize("math", [0, 1])
+def test_gemv_fp8(pkg, g, N, K, math):
+    pkg.debug_set_math(-1, math)
+    w = onp.seeded_bf16(5000 + N + K, (N, K), 0.02)
+    q, sc = onp.make_fp8_weight(w)
+    x = onp.seeded_bf16(6000 + N + K, (K,), 1.0)
+    got = run_fp8(pkg, g, q, sc, x)
+    check_close(got, onp.linear_fp8(q, sc, x), abs_floor=1e-4, what=f"fp8 N={N} K={K}")
+    assert np.array_equal(got, run_fp8(pkg, g, q, sc, x, pdl=True))
+    pkg.debug_set_math(-1, 1)
+
+
+@pytest.mark.parametrize("math", [0, 1])
+def test_gemv_fp8_whole_code_space(pkg, g, math):
+    """Every byte value as a weight (subnormals, negative zero, the two NaN
+    codes that decode to +/-480), scales in [1e-3, 1], x in [-1.5, 1.5]: the
+    recipe of native/tests/kernel_ops.cpp:834-850, checked against the
+    double-accumulate statement."""
+    pkg.debug_set_math(-1, math)
+    rng = np.random.default_rng(0xF0E1)
+    N, K = 256, 2048
+    q = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    sc = rng.uniform(1e-3, 1.0, N).astype(np.float32)
+    x = onp.f32_to_bf16(rng.uniform(-1.5, 1.5, K).astype(np.float32))
+    ref = onp.f32_to_bf16(onp.linear_f64(onp.e4m3_to_f32(q), x, sc))
+    check_close(run_fp8(pkg, g, q, sc, x), ref, abs_floor=1e-4, what="fp8 all codes")
+    pkg.debug_set_math(-1, 1)
+
+
+# ---- fused variants ----------------------------------------------------------------------
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("N,n,with_add", [(2560, 2048, True), (QKV_B, K_B, True), (64, 512, False)])
+def test_prologue_resnorm(pkg, g, fp8, N, n, with_add):
+    w = onp.seeded_bf16(70 + N, (N, n), 0.02)
+    res = onp.seeded_bf16(71 + N, (n,), 1.3)
+    add = onp.seeded_bf16(72 + N, (n,), 0.7) if with_add else None
+    nw = onp.seeded_bf16(73 + N, (n,), 1.0)
+    res_o = onp.add_bf16(res, add) if with_add else res
+    h = onp.rmsnorm_bf16(nw, res_o)
+    d_res_out, dy = g.empty_u16(n), g.empty_u16(N)
+    args = (g.dev(res), g.dev(add) if with_add else None, g.dev(nw), d_res_out, dy, N, n, 1e-6)
+    if fp8:
+        q, sc = onp.make_fp8_weight(w)
+        pkg.launch_gemv_fp8_prologue(g.dev(q), g.dev(sc), *args)
+        ref = onp.linear_fp8(q, sc, h)
+    else:
+        pkg.launch_gemv_rows_prologue(g.dev(w), *args)
+        ref = onp.linear_bf16(w, h)
+    g.sync()
+    assert np.array_equal(g.host_u16(d_res_out), res_o), "residual must be bit-exact"
+    check_close(g.host_u16(dy), ref, abs_floor=4e-3, what=f"prologue fp8={fp8} N={N}")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("N,K", [(2048, 6144), (K_B, I_B), (40, 256)])
+def test_prologue_swiglu(pkg, g, fp8, N, K):
+    w = onp.seeded_bf16(80 + N, (N, K), 0.02)
+    gu = onp.seeded_bf16(81 + N, (2 * K,), 1.0)
+    h = onp.swiglu_bf16(gu[:K], gu[K:])
+    dy = g.empty_u16(N)
+    if fp8:
+        q, sc = onp.make_fp8_weight(w)
+        pkg.launch_gemv_fp8_swiglu(g.dev(q), g.dev(sc), g.dev(gu), dy, N, K)
+        ref = onp.linear_fp8(q, sc, h)
+    else:
+        pkg.launch_gemv_rows_swiglu(g.dev(w), g.dev(gu), dy, N, K)
+        ref = onp.linear_bf16(w, h)
+    g.sync()
+    check_close(g.host_u16(dy), ref, abs_floor=4e-3, what=f"swiglu-in fp8={fp8} N={N}")
+
+
+def interleaved(g, pkg, arr, I):
+    src = g.dev(arr)
+    dst = torch.empty_like(src)
+    pkg.interleave_rows(src, dst, I, arr.strides[0])
+    g.sync()
+    out = dst.cpu().numpy().view(arr.dtype)
+    want = np.empty_like(arr)
+    want[0::2], want[1::2] = arr[:I], arr[I:]
+    assert np.array_equal(out, want), "interleave must be a pure permutation"
+    return dst
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("M,I,K", [(1, I_B, K_B), (1, 6144, 2048), (2, 96, 256), (3, 1000, 2048), (4, I_B, K_B)])
+def test_gate_up_swiglu_epilogue(pkg, g, golden, fp8, M, I, K):
+    base = M == 1 and I == I_B
+    w = onp.seeded_bf16(onp.SEED_BASE + 2000 if base else 90 + I, (2 * I, K), 0.02)
+    x = onp.seeded_bf16(onp.SEED_BASE + 2001 if base else 91 + I, (K,) if M == 1 else (M, K), 1.0)
+    dy = g.empty_u16(M, I)
+    if fp8:
+        q, sc = onp.make_fp8_weight(w)
+        dq, ds = interleaved(g, pkg, q, I), interleaved(g, pkg, sc.reshape(-1, 1), I)
+        pkg.launch_gate_up_swiglu(dq, ds, g.dev(x), dy, M, 2 * I, K)
+        ref = onp.gate_up_swiglu_fp8(q, sc, x)
+    else:
+        pkg.launch_gate_up_swiglu(interleaved(g, pkg, w, I), None, g.dev(x), dy, M, 2 * I, K)
+        ref = onp.gate_up_swiglu_bf16(w, x)
+    g.sync()
+    # a 1-ulp flip of gate or up before the SwiGLU moves the product by about an ulp as well
+    check_close(g.host_u16(dy), ref, abs_floor=4e-3, what=f"gate_up epilogue fp8={fp8} M={M} I={I}")
+    if base:
+        key = "c2_y" if fp8 else "c2_y_bf16w"
+        check_close(g.host_u16(dy), golden["baseline"][key], abs_floor=4e-3, what="config2 vs reference output")
+
+
+# ---- batched -------------------------------------------------------------------------------
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 16, 32, 64])
+@pytest.mark.parametrize("N,K", [(K_B, I_B), (2048, 6144), (264, 512)])
+def test_gemm_bf16(pkg, g, golden, M, N, K):
+    base = (N, K) == (K_B, I_B)
+    w = onp.seeded_bf16(onp.SEED_BASE + 3000 if base else 100 + N, (N, K), 0.02)
+    if base:
+        rng = np.random.default_rng(onp.SEED_BASE + 3001)
+        X = onp.f32_to_bf16(rng.standard_normal((64, K), dtype=np.float32) * np.float32(0.5))[:M]
+    else:
+        X = onp.seeded_bf16(101 + N, (M, K), 0.5)
+    ws_bytes = pkg.gemm_workspace_bytes(M, N, K)
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device="cuda")
+    dc = g.empty_u16(M, N)
+    pkg.gemm_bf16(None, ws, ws_bytes, M, N, K, g.dev(w), g.dev(X), dc)
+    g.sync()
+    check_close(g.host_u16(dc), onp.linear_bf16(w, X), what=f"gemm_bf16 M={M} N={N} K={K}")
+    if base and f"c3_y_bf16_m{M}" in golden["baseline"]:
+        check_close(g.host_u16(dc), golden["baseline"][f"c3_y_bf16_m{M}"], what=f"config3 bf16 M={M} vs reference")
+
+
+@pytest.mark.parametrize("M", [2, 3, 4, 7, 8, 16, 32, 64])
+@pytest.mark.parametrize("N,K", [(K_B, I_B), (2560, 2048), (24, 2048), (64, 100)])
+def test_gemv_fp8_rows_m(pkg, g, golden, M, N, K):
+    base = (N, K) == (K_B, I_B)
+    w = onp.seeded_bf16(onp.SEED_BASE + 3000 if base else 110 + N, (N, K), 0.02)
+    q, sc = onp.make_fp8_weight(w)
+    if base:
+        rng = np.random.default_rng(onp.SEED_BASE + 3001)
+        X = onp.f32_to_bf16(rng.standard_normal((64, K), dtype=np.float32) * np.float32(0.5))[:M]
+    else:
+        X = onp.seeded_bf16(111 + N, (M, K), 0.5)
+    dq, ds = g.dev(q), g.dev(sc)
+    dy = g.empty_u16(M, N)
+    pkg.launch_gemv_fp8_rows_m(dq, ds, g.dev(X), dy, M, N, K)
+    g.sync()
+    got = g.host_u16(dy)
+    check_close(got, onp.linear_fp8(q, sc, X), abs_floor=1e-4, what=f"fp8 rows_m M={M} N={N} K={K}")
+    if base and f"c3_y_fp8_m{M}" in golden["baseline"]:
+        check_close(got, golden["baseline"][f"c3_y_fp8_m{M}"], abs_floor=1e-4, what=f"config3 fp8 M={M} vs reference")
+    if M <= 4:   # CUDA-core rows: each row bit-equal to the M=1 call (the reference's anchor, gemv_fp8.cu:533-607)
+        for m in range(M):
+            assert np.array_equal(got[m], run_fp8(pkg, g, q, sc, X[m])), f"row {m} differs from the solo call"
+
+
+# ---- greedy ---------------------------------------------------------------------------------
+def test_argmax_tie_and_edges(pkg, g, golden):
+    lg = golden["small"]["am_logits"]
+    stage = torch.empty(pkg.argmax_stage_bytes(4), dtype=torch.uint8, device="cuda")
+    out = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+    val = torch.zeros(4, dtype=torch.float32, device="cuda")
+    pkg.launch_argmax_bf16(g.dev(lg), 1, lg.size, lg.size, 0, stage, out, val)
+    g.sync()
+    assert out[0].item() == int(golden["small"]["am_idx"]) == 17 and val[0].item() == 50.0
+    rows = onp.seeded_bf16(9, (4, 130560), 3.0)
+    rows[1, :] = 0xFF80                       # all -inf -> index 0
+    rows[2, 130559] = onp.f32_to_bf16(np.array([99.0], np.float32))[0]   # last element wins
+    rows[3, 5] = rows[3, 70000] = onp.f32_to_bf16(np.array([77.0], np.float32))[0]
+    pkg.launch_argmax_bf16(g.dev(rows), 4, 130560, 130560, 1000, stage, out, val)
+    g.sync()
+    want = [onp.greedy(rows[i]) + 1000 for i in range(4)]
+    assert out.tolist() == want and want[1] == 1000 and want[2] == 130559 + 1000 and want[3] == 1005
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("M,N,K", [(1, 4001, 512), (3, 10007, 2048), (4, 130560 // 8, 2048)])
+def test_lm_head_argmax_small(pkg, g, fp8, M, N, K):
+    w = onp.seeded_bf16(120 + N, (N, K), 0.02)
+    x = onp.seeded_bf16(121 + N, (M, K), 1.0)
+    stage = torch.empty(pkg.argmax_stage_bytes(M), dtype=torch.uint8, device="cuda")
+    idx = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    val = torch.zeros(M, dtype=torch.float32, device="cuda")
+    dl = g.empty_u16(M, N)
+    if fp8:
+        q, sc = onp.make_fp8_weight(w)
+        pkg.launch_lm_head_argmax(g.dev(q), g.dev(sc), g.dev(x), dl, N, M, N, K, 7, stage, idx, val)
+        ref = onp.linear_fp8(q, sc, x)
+    else:
+        pkg.launch_lm_head_argmax(g.dev(w), None, g.dev(x), dl, N, M, N, K, 7, stage, idx, val)
+        ref = onp.linear_bf16(w, x)
+    g.sync()
+    got = g.host_u16(dl)
+    check_close(got, ref, abs_floor=1e-4 if fp8 else 1e-3, what=f"lm_head logits fp8={fp8}")
+    # the fused argmax must agree exactly with an argmax over the logits the GPU itself wrote
+    assert idx.tolist() == [onp.greedy(got[m]) + 7 for m in range(M)]
+    assert val.tolist() == [float(onp.bf16_to_f32(got[m]).max()) for m in range(M)]
+
+
+def test_lm_head_config4_against_reference_fixture(pkg, g, golden):
+    """vocab 122753 x 2304 (not a multiple of anything), M = 1 and 8."""
+    gb = golden["baseline"]
+    w = onp.seeded_bf16(onp.SEED_BASE + 4000, (V_B, K_B), 0.02)
+    X = onp.seeded_bf16(onp.SEED_BASE + 4001, (8, K_B), 1.0)
+    dw = g.dev(w)
+    for M in (1, 8):
+        stage = torch.empty(pkg.argmax_stage_bytes(M), dtype=torch.uint8, device="cuda")
+        idx = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+        dl = g.empty_u16(M, V_B)
+        pkg.launch_lm_head_argmax(dw, None, g.dev(X[:M]), dl, V_B, M, V_B, K_B, 0, stage, idx, None)
+        g.sync()
+        got = g.host_u16(dl)
+        check_close(got[0], gb["c4_logits_m0"], what=f"config4 logits M={M}")
+        for m in range(M):
+            assert idx[m].item() == onp.greedy(got[m])
+            if gb["c4_top2_gap"][m] > 0.05:      # clear winner: must equal the reference's token
+                assert idx[m].item() == int(gb["c4_argmax"][m])
+
+
+# ---- W8A8 pieces ---------------------------------------------------------------------------
+def test_quant_rows_byte_exact(pkg, g):
+    x = onp.seeded_bf16(130, (5, 2048), 1.0)
+    x[2] = 0
+    dq = torch.zeros((5, 2048), dtype=torch.uint8, device="cuda")
+    ds = torch.zeros(5, dtype=torch.float32, device="cuda")
+    pkg.launch_quant_rows(g.dev(x), dq, ds, 5, 2048)
+    g.sync()
+    q, s = onp.quant_rows_e4m3(x)
+    assert np.array_equal(dq.cpu().numpy(), q)
+    assert np.array_equal(ds.cpu().numpy().view(np.uint32), s.view(np.uint32))
+
+
+def test_post_scale_rows(pkg, g):
+    y = onp.seeded_bf16(131, (3, 40), 1.0)
+    ws = np.random.default_rng(1).uniform(0.5, 2, 40).astype(np.float32)
+    xs = np.random.default_rng(2).uniform(0.5, 2, 3).astype(np.float32)
+    dy = g.dev(y)
+    pkg.launch_post_scale_rows(dy, g.dev(ws), g.dev(xs), 3, 40)
+    g.sync()
+    want = onp.f32_to_bf16(onp.bf16_to_f32(y) * (ws[None, :] * xs[:, None]))
+    assert np.array_equal(g.host_u16(dy), want)
+
+
+# ---- host-buffer call ------------------------------------------------------------------------
+def test_linear_host(pkg, g):
+    N, K = 512, 2304
+    w = onp.seeded_bf16(140, (N, K), 0.02)
+    x = onp.seeded_bf16(141, (K,), 1.0)
+    hx = torch.from_numpy(x.view(np.int16)).pin_memory()
+    hy = torch.zeros(N, dtype=torch.int16).pin_memory()
+    pkg.linear_host(0, g.dev(w), None, hx, hy, 1, N, K, g.empty_u16(K), g.empty_u16(N))
+    check_close(hy.numpy().view(np.uint16), onp.linear_bf16(w, x), what="linear_host")
+
+
+def test_errors_are_reported_not_swallowed(pkg, g):
+    w = g.dev(onp.seeded_bf16(1, (8, 16), 0.02))
+    with pytest.raises(pkg.McError) as e:
+        pkg.launch_decode_gemv(w, w, w, 8, 12, 1)          # K % 8 != 0
+    assert e.value.status == pkg.MC_E_INVALID_ARGUMENT and "K=12" in e.value.message
