@@ -91,6 +91,22 @@ MC_SM100_API mc_status_t mc_sm100_decode_gemv(const uint16_t* d_w, const uint16_
                                  uint32_t N, uint32_t K, int32_t tactic, uint32_t split_s,
                                  float* d_split_partial, void* stream, int32_t pdl);
 
+/* Split-K bf16 GEMV for callers that cannot allocate device memory (a frozen
+ * arena, a step replayed from a graph, a plugin host without an allocator).
+ * This entry point has no counterpart in the reference.  Same arithmetic and
+ * result as mc_sm100_decode_gemv with tactic SPLITK, but the fp32 partials live
+ * in a 512 KiB array that is part of the library image, so split_s * N must
+ * not exceed 131072 (MC_E_UNSUPPORTED otherwise).  It calls no allocator of
+ * any kind.  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress, that device current); make that call before any stream
+ * capture.  All calls share the one array: two calls that overlap on the GPU
+ * (different streams, or the same graph replayed concurrently) race; calls
+ * ordered on one stream are safe, and no call depends on what an earlier call
+ * left in the array. */
+MC_SM100_API mc_status_t mc_sm100_decode_gemv_splitk_static(const uint16_t* d_w, const uint16_t* d_x,
+                                                            uint16_t* d_y, uint32_t N, uint32_t K,
+                                                            uint32_t split_s, void* stream, int32_t pdl);
+
 /* y[N] = bf16( scale[n] * sum_k e4m3(W[n,k]) * x[k] ); the row scale multiplies
  * the finished fp32 sum once.  Replaces launch_gemv_fp8
  * (native/kernels/sm120/kernels.h:721-726, gemv_fp8.cu:694-721).  Any K; the
@@ -261,6 +277,7 @@ MC_SM100_API mc_status_t mc_sm100_linear_host(int32_t kind, const void* d_w, con
  * 0 = widen to fp32 then FFMA, 1 = mixed-precision FMA on bf16 operands;
  * any other value keeps the current form.  Both forms give identical bits. */
 MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
+
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,7 @@ SIGNATURES = {
     "mc_sm100_last_error": (C.c_char_p, []),
     "mc_sm100_device_check": (_i32, [C.POINTER(_i32), C.POINTER(C.c_uint64), C.POINTER(_i32), C.POINTER(_i32)]),
     "mc_sm100_decode_gemv": (_i32, [_vp, _vp, _vp, _u32, _u32, _i32, _u32, _vp, _vp, _i32]),
+    "mc_sm100_decode_gemv_splitk_static": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _i32]),
     "mc_sm100_gemv_fp8": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _i32]),
     "mc_sm100_gemv_rows_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
     "mc_sm100_gemv_fp8_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
@@ -118,6 +119,10 @@ def device_check():
 def launch_decode_gemv(w, x, y, N, K, tactic=TACTIC_ROWS, split_s=0, split_partial=None, stream=None, pdl=False):
     _check(lib().mc_sm100_decode_gemv(_p(w), _p(x), _p(y), N, K, tactic, split_s, _p(split_partial),
                                       _stream(stream), int(pdl)))
+
+
+def launch_decode_gemv_splitk_static(w, x, y, N, K, split_s, stream=None, pdl=False):
+    _check(lib().mc_sm100_decode_gemv_splitk_static(_p(w), _p(x), _p(y), N, K, split_s, _stream(stream), int(pdl)))
 
 
 def launch_gemv_fp8(w, scale, x, y, N, K, stream=None, pdl=False):
@@ -216,3 +221,4 @@ def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=N
 
 def debug_set_math(bf16_math=-1, fp8_math=-1):
     lib().mc_sm100_debug_set_math(bf16_math, fp8_math)
+
