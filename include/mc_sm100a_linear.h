@@ -278,6 +278,10 @@ MC_SM100_API mc_status_t mc_sm100_linear_host(int32_t kind, const void* d_w, con
  * any other value keeps the current form.  Both forms give identical bits. */
 MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
 
+/* Every wait inside the tensor-core kernel is bounded; a wait that runs out
+ * makes the kernel skip its stores and raise a device-side flag.  This reads
+ * the flag (synchronising copy) and clears it: 0 = no wait ever ran out. */
+MC_SM100_API int32_t mc_sm100_debug_take_error(void);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,7 @@ SIGNATURES = {
                                                 _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_linear_host": (_i32, [_i32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
+    "mc_sm100_debug_take_error": (_i32, []),
 }
 
 
@@ -222,3 +223,6 @@ def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=N
 def debug_set_math(bf16_math=-1, fp8_math=-1):
     lib().mc_sm100_debug_set_math(bf16_math, fp8_math)
 
+
+def debug_take_error() -> int:
+    return lib().mc_sm100_debug_take_error()

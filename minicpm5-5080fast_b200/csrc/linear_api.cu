@@ -238,6 +238,8 @@ void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math) {
     if (fp8_math == 0 || fp8_math == 1) g_math[1].store(fp8_math);
 }
 
+int32_t mc_sm100_debug_take_error(void) { return skinny_take_error(); }
+
 mc_status_t mc_sm100_device_check(int32_t* out_sm_count, uint64_t* out_l2_bytes,
                                   int32_t* out_cc_major, int32_t* out_cc_minor) {
     clear_error();

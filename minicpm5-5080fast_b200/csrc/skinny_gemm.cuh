@@ -22,4 +22,7 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
                         const float* x_scale, uint16_t* y, uint32_t M, uint32_t N, uint32_t K,
                         void* workspace, size_t ws_size, cudaStream_t stream, bool pdl);
 
+// 1 when a bounded wait inside the tensor-core kernel ran out since the last query (clears it), -1 on a CUDA error.
+int skinny_take_error();
+
 }  // namespace mcl
