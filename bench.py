@@ -39,16 +39,12 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
 
-def roundup(a, b):
-    return (a + b - 1) // b * b
+import importlib.util as _ilu
 
-
-def shard_rows(n, world, rank, mult=8):
-    """Rows [lo, hi) of an N-row matrix owned by `rank`; shards are equal and a
-    multiple of `mult` except the last, which may be short or empty."""
-    per = roundup((n + world - 1) // world, mult)
-    lo = min(n, rank * per)
-    return lo, min(n, lo + per), per
+_spec = _ilu.spec_from_file_location("mc_sharding", os.path.join(ROOT, "minicpm5-5080fast_b200", "sharding.py"))
+_sh = _ilu.module_from_spec(_spec)
+_spec.loader.exec_module(_sh)
+roundup, shard_rows = _sh.roundup, _sh.shard_rows
 
 
 def linear_bytes(n, k, m, wb, n_out=None):

@@ -151,7 +151,7 @@ MC_SM100_API mc_status_t mc_sm100_gemv_fp8_swiglu(const uint8_t* d_w, const floa
  * swiglu_gated_kernel (native/kernels/sm120/swiglu.cu:57-70;
  * tools/reference_forward.py:293-294).  d_scale == NULL selects bf16 weights
  * (d_w read as uint16_t), otherwise e4m3 weights with interleaved row scales.
- * M in [1,4]; x [M,K], y [M, N/2]. */
+ * M in [1,64] (CUDA cores up to 4 rows, tcgen05 above); x [M,K], y [M, N/2]. */
 MC_SM100_API mc_status_t mc_sm100_gate_up_swiglu(const void* d_w_interleaved, const float* d_scale_interleaved,
                                     const uint16_t* d_x, uint16_t* d_y, uint32_t M, uint32_t N,
                                     uint32_t K, void* stream, int32_t pdl);
@@ -185,9 +185,10 @@ MC_SM100_API mc_status_t mc_sm100_gemv_fp8_rows_m(const uint8_t* d_w, const floa
 /* C[M,N] = bf16( B[M,K] . A[N,K]^T ): d_a is the WEIGHT [N,K], d_b the
  * activation [M,K], both row-major (operand order of GemmEngine::gemm_bf16,
  * native/runtime/gemm.h:3-11, 61-63; native/runtime/gemm.cpp:316-380).
- * M in [1,64].  workspace: fp32 split-K partials, at least
- * mc_sm100_gemm_workspace_bytes(M,N,K) bytes (the reference passes its 16 MB
- * per-session workspace here); may be NULL when that function returns 0. */
+ * M in [1,64].  workspace: kept for signature compatibility (the reference
+ * passes its 16 MB per-session workspace here); split-K partials are reduced
+ * through distributed shared memory inside a thread-block cluster, so
+ * mc_sm100_gemm_workspace_bytes returns 0 and NULL is accepted. */
 MC_SM100_API mc_status_t mc_sm100_gemm_bf16(void* stream, void* d_workspace, size_t ws_size, uint32_t M,
                                uint32_t N, uint32_t K, const void* d_a, const void* d_b,
                                void* d_c);
@@ -216,6 +217,17 @@ MC_SM100_API mc_status_t mc_sm100_quant_rows(const uint16_t* d_x, uint8_t* d_xq,
 MC_SM100_API mc_status_t mc_sm100_post_scale_rows(uint16_t* d_y, const float* d_w_scale,
                                      const float* d_x_scale, uint32_t M, uint32_t N,
                                      void* stream);
+
+/* Batched residual add + RMSNorm between the batched GEMMs: res[r,:] =
+ * bf16(res + add) in place (add may be NULL), out[r,:] = bf16(res * rsqrt(mean
+ * (res^2) + eps) * w) on the rounded residual.  The M = 1 chain has this fused
+ * into the GEMV prologue; the batched chain calls it like the reference's
+ * BatchGroup does (launch_residual_add_rmsnorm, native/kernels/sm120/rmsnorm.cu:130-166;
+ * native/runtime/batch_group.cpp:770, 794). */
+MC_SM100_API mc_status_t mc_sm100_residual_rmsnorm_rows(uint16_t* d_res, const uint16_t* d_add,
+                                                        const uint16_t* d_norm_w, uint16_t* d_out,
+                                                        uint32_t rows, uint32_t n, float eps,
+                                                        void* stream, int32_t pdl);
 
 /* ------------------------------------------------------- lm_head / greedy --- */
 
@@ -274,8 +286,10 @@ MC_SM100_API mc_status_t mc_sm100_linear_host(int32_t kind, const void* d_w, con
 /* Not part of the frozen surface (same standing as the reference's
  * mc_debug_* exports, native/runtime/session.cpp:631-723): selects the
  * arithmetic form of the streaming kernels per weight type for A/B runs.
- * 0 = widen to fp32 then FFMA, 1 = mixed-precision FMA on bf16 operands;
- * any other value keeps the current form.  Both forms give identical bits. */
+ * 0 = widen to fp32 then FFMA, 1 = mixed-precision FMA on bf16 operands (both
+ * in the generic M <= 4 kernel), 2 = the decode-chain M = 1 kernel (default);
+ * any other value keeps the current form.  Forms 0 and 1 give identical bits;
+ * form 2 sums in a different order (same contract, same tolerance). */
 MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
 
 /* Every wait inside the tensor-core kernel is bounded; a wait that runs out

@@ -51,6 +51,7 @@ SIGNATURES = {
     "mc_sm100_gemm_fp8": (_i32, [_vp, _vp, C.c_size_t, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_sm100_quant_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp]),
     "mc_sm100_post_scale_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mc_sm100_residual_rmsnorm_rows": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _i32]),
     "mc_sm100_argmax_bf16": (_i32, [_vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_argmax_stage_bytes": (C.c_size_t, [_u32]),
     "mc_sm100_lm_head_argmax": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
@@ -190,6 +191,10 @@ def launch_quant_rows(x, xq, scale, M, K, stream=None):
 
 def launch_post_scale_rows(y, w_scale, x_scale, M, N, stream=None):
     _check(lib().mc_sm100_post_scale_rows(_p(y), _p(w_scale), _p(x_scale), M, N, _stream(stream)))
+
+
+def launch_residual_rmsnorm_rows(res, add, norm_w, out, rows, n, eps, stream=None, pdl=False):
+    _check(lib().mc_sm100_residual_rmsnorm_rows(_p(res), _p(add), _p(norm_w), _p(out), rows, n, eps, _stream(stream), int(pdl)))
 
 
 def argmax_stage_bytes(n_rows) -> int:

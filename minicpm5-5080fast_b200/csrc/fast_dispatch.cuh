@@ -1,0 +1,92 @@
+// fast_dispatch.cuh -- picks a tile shape of gemv_fast_kernel for an M = 1 call.
+//
+// The shape decides how much of the matrix is in flight before
+// griddepcontrol.wait.  Small matrices get a shape whose warps cover every row
+// in ONE round (all loads issued, and where registers allow also widened, before
+// the wait); large matrices use the widest CTA and walk their rows in rounds.
+#pragma once
+
+#include "gemv_fast.cuh"
+
+namespace mcl {
+
+template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int T>
+inline mc_status_t launch_fast_one(const RowsArgs& a, cudaStream_t stream, bool pdl) {
+    auto kern = gemv_fast_kernel<WB, R, U, PRE, DB, PRO, EPI, T>;
+    const size_t smem = (size_t)a.K * (WB == 1 ? 4u : 2u) + (PRO == PRO_RESNORM ? (size_t)a.K * 4u : 0u);
+    static size_t smem_set = 48u * 1024u;
+    if (smem > smem_set) {
+        if (smem > 200u * 1024u) {
+            set_error("gemv: activation of %zu bytes does not fit in shared memory", smem);
+            return MC_E_UNSUPPORTED;
+        }
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error("gemv: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+            return MC_E_CUDA;
+        }
+        smem_set = smem;
+    }
+    const uint32_t groups = (a.N + R - 1) / R;
+    uint32_t gx = (uint32_t)sm_count();
+    if (groups < gx) gx = groups;
+    if (EPI == EPI_ARGMAX && gx > kArgmaxCands) gx = kArgmaxCands;
+    (void)launch(kern, dim3(gx), dim3(T), smem, stream, pdl, a);
+    MCL_CHECK_LAUNCH("gemv_fast");
+    return MC_OK;
+}
+
+// R = 1 epilogues (store, argmax)
+template <int WB, int PRO, int EPI>
+inline mc_status_t launch_fast_rows(const RowsArgs& a, cudaStream_t stream, bool pdl) {
+    const uint32_t per_lane = (a.K * WB / 16u + 31u) / 32u;
+    const uint32_t sms = (uint32_t)sm_count();
+    if constexpr (WB == 2) {
+        if (per_lane <= 9) {
+            if (a.N <= 24u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 768>(a, stream, pdl);
+            return launch_fast_one<2, 1, 9, false, true, PRO, EPI, 512>(a, stream, pdl);   // two rows in flight per warp
+        }
+        if (per_lane <= 24 && a.N <= 16u * sms) return launch_fast_one<2, 1, 24, false, false, PRO, EPI, 512>(a, stream, pdl);
+        return launch_fast_one<2, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
+    } else {
+        if (per_lane <= 5) {
+            if (a.N <= 24u * sms) return launch_fast_one<1, 1, 5, true, false, PRO, EPI, 768>(a, stream, pdl);
+            return launch_fast_one<1, 1, 5, false, true, PRO, EPI, 1024>(a, stream, pdl);
+        }
+        if (per_lane <= 12 && a.N <= 16u * sms) return launch_fast_one<1, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
+        return launch_fast_one<1, 1, 6, false, false, PRO, EPI, 1024>(a, stream, pdl);
+    }
+}
+
+// R = 2: SwiGLU epilogue over interleaved (gate, up) rows
+template <int WB, int PRO>
+inline mc_status_t launch_fast_pairs(const RowsArgs& a, cudaStream_t stream, bool pdl) {
+    const uint32_t per_lane = (a.K * WB / 16u + 31u) / 32u;
+    if constexpr (WB == 2) {
+        if (per_lane <= 9) return launch_fast_one<2, 2, 9, false, true, PRO, EPI_SWIGLU, 256>(a, stream, pdl);
+        return launch_fast_one<2, 2, 12, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
+    } else {
+        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, true, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
+        return launch_fast_one<1, 2, 6, false, false, PRO, EPI_SWIGLU, 1024>(a, stream, pdl);
+    }
+}
+
+// Entry of one translation unit (fast_inst_w*.cu).
+template <int WB>
+mc_status_t launch_fast(int pro, int epi, const RowsArgs& a, cudaStream_t stream, bool pdl);
+
+#define MCL_DEFINE_LAUNCH_FAST(WBV)                                                                  \
+    template <>                                                                                      \
+    mc_status_t launch_fast<WBV>(int pro, int epi, const RowsArgs& a, cudaStream_t stream, bool pdl) { \
+        if (pro == PRO_NONE && epi == EPI_STORE) return launch_fast_rows<WBV, PRO_NONE, EPI_STORE>(a, stream, pdl);       \
+        if (pro == PRO_NONE && epi == EPI_ARGMAX) return launch_fast_rows<WBV, PRO_NONE, EPI_ARGMAX>(a, stream, pdl);     \
+        if (pro == PRO_NONE && epi == EPI_SWIGLU) return launch_fast_pairs<WBV, PRO_NONE>(a, stream, pdl);                \
+        if (pro == PRO_RESNORM && epi == EPI_STORE) return launch_fast_rows<WBV, PRO_RESNORM, EPI_STORE>(a, stream, pdl); \
+        if (pro == PRO_RESNORM && epi == EPI_ARGMAX) return launch_fast_rows<WBV, PRO_RESNORM, EPI_ARGMAX>(a, stream, pdl); \
+        if (pro == PRO_RESNORM && epi == EPI_SWIGLU) return launch_fast_pairs<WBV, PRO_RESNORM>(a, stream, pdl);          \
+        if (pro == PRO_SWIGLU && epi == EPI_STORE) return launch_fast_rows<WBV, PRO_SWIGLU, EPI_STORE>(a, stream, pdl);   \
+        set_error("gemv: no kernel for prologue=%d epilogue=%d", pro, epi);                          \
+        return MC_E_UNSUPPORTED;                                                                     \
+    }
+
+}  // namespace mcl

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstring>
 
+#include "fast_dispatch.cuh"
 #include "rows_dispatch.cuh"
 #include "skinny_gemm.cuh"
 
@@ -33,14 +34,21 @@ int sm_count() {
     return v;
 }
 
-// Math form per weight type (index = bytes per weight element).  Both forms are
-// compiled; the default is the measured winner and the debug hook below lets a
-// benchmark flip it.
-static std::atomic<int> g_math[3] = {{0}, {MATH_MIXED}, {MATH_MIXED}};
+// Kernel form per weight type (index = bytes per weight element): 2 = the
+// decode-chain kernel (gemv_fast_kernel, M = 1 only), 1 / 0 = gemv_rows_kernel with
+// mixed-precision FMA / widen-then-FFMA.  All forms are compiled; the default is the
+// measured winner and the debug hook lets a benchmark flip it.
+constexpr int FORM_FAST = 2;
+static std::atomic<int> g_math[3] = {{0}, {FORM_FAST}, {FORM_FAST}};
 
 static mc_status_t rows(int wb, int M, int pro, int epi, const RowsArgs& a, uint32_t splits,
                         cudaStream_t st, bool pdl) {
-    const int math = g_math[wb].load(std::memory_order_relaxed);
+    int math = g_math[wb].load(std::memory_order_relaxed);
+    if (math == FORM_FAST) {
+        if (M == 1 && epi != EPI_PARTIAL && splits == 1)
+            return wb == 2 ? launch_fast<2>(pro, epi, a, st, pdl) : launch_fast<1>(pro, epi, a, st, pdl);
+        math = MATH_MIXED;
+    }
     if (wb == 2)
         return math == MATH_MIXED ? launch_rows<2, MATH_MIXED>(M, pro, epi, a, splits, st, pdl)
                                   : launch_rows<2, MATH_CVT>(M, pro, epi, a, splits, st, pdl);
@@ -220,6 +228,38 @@ __global__ void post_scale_rows_kernel(uint16_t* __restrict__ y, const float* __
     }
 }
 
+// res[r,:] = bf16(res[r,:] + add[r,:]) in place (add may be null), then
+// out[r,:] = bf16( res * rsqrt(mean(res^2) + eps) * w ) on the ROUNDED residual; one
+// CTA per row (semantics of native/kernels/sm120/rmsnorm.cu:130-166).
+__global__ void residual_rmsnorm_rows_kernel(uint16_t* __restrict__ res, const uint16_t* __restrict__ add,
+                                             const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
+                                             uint32_t n, float eps) {
+    __shared__ float part[8];
+    pdl_trigger();
+    pdl_wait();
+    uint16_t* rr = res + (size_t)blockIdx.x * n;
+    const uint16_t* ar = add ? add + (size_t)blockIdx.x * n : nullptr;
+    uint16_t* orow = out + (size_t)blockIdx.x * n;
+    float ss = 0.f;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float r = __uint_as_float((uint32_t)rr[i] << 16);
+        if (ar != nullptr) {
+            const uint16_t rb = f32_to_bf16_bits(r + __uint_as_float((uint32_t)ar[i] << 16));
+            rr[i] = rb;
+            r = __uint_as_float((uint32_t)rb << 16);
+        }
+        ss = fmaf(r, r, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0u) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (uint32_t k = 0; k < blockDim.x / 32u; ++k) tot += part[k];
+    const float inv = 1.0f / sqrtf(tot / (float)n + eps);
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x)   // each thread re-reads only what it wrote
+        orow[i] = f32_to_bf16_bits(__uint_as_float((uint32_t)rr[i] << 16) * inv * __uint_as_float((uint32_t)w[i] << 16));
+}
+
 }  // namespace mcl
 
 using namespace mcl;
@@ -234,8 +274,8 @@ const char* mc_sm100_last_error(void) { return g_err; }
 // Debug hook (not part of the frozen surface, like the reference's mc_debug_*):
 // selects the math form per weight type; -1 keeps the current one.
 void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math) {
-    if (bf16_math == 0 || bf16_math == 1) g_math[2].store(bf16_math);
-    if (fp8_math == 0 || fp8_math == 1) g_math[1].store(fp8_math);
+    if (bf16_math >= 0 && bf16_math <= 2) g_math[2].store(bf16_math);
+    if (fp8_math >= 0 && fp8_math <= 2) g_math[1].store(fp8_math);
 }
 
 int32_t mc_sm100_debug_take_error(void) { return skinny_take_error(); }
@@ -384,11 +424,14 @@ mc_status_t mc_sm100_gate_up_swiglu(const void* d_w, const float* d_scale, const
                                     int32_t pdl) {
     clear_error();
     const int wb = d_scale == nullptr ? 2 : 1;
-    if (d_w == nullptr || d_x == nullptr || d_y == nullptr || M == 0 || M > 4u || N == 0 || (N & 1u) != 0 ||
+    if (d_w == nullptr || d_x == nullptr || d_y == nullptr || M == 0 || M > 64u || N == 0 || (N & 1u) != 0 ||
         K == 0 || (K % (wb == 2 ? 8u : 16u)) != 0 || !aligned16(d_w) || !aligned16(d_x)) {
         set_error("mc_sm100_gate_up_swiglu: invalid args (M=%u N=%u K=%u)", M, N, K);
         return MC_E_INVALID_ARGUMENT;
     }
+    if (M > 4u)
+        return skinny_gemm(wb == 2 ? SKINNY_W_BF16 : SKINNY_W_E4M3, d_w, d_scale, d_x, nullptr, d_y, M, N, K, true,
+                           (cudaStream_t)stream, pdl != 0);
     RowsArgs a{};
     a.w = d_w; a.scale = d_scale; a.x = d_x; a.y = d_y; a.N = N; a.K = K; a.y_stride = N / 2u; a.kseg = K;
     return rows(wb, (int)M, PRO_NONE, EPI_SWIGLU, a, 1, (cudaStream_t)stream, pdl != 0);
@@ -448,7 +491,7 @@ mc_status_t mc_sm100_gemv_fp8_rows_m(const uint8_t* d_w, const float* d_scale, c
         }
         return MC_OK;
     }
-    return skinny_gemm(SKINNY_W_E4M3, d_w, d_scale, d_x, nullptr, d_y, M, N, K, nullptr, 0, st, pdl != 0);
+    return skinny_gemm(SKINNY_W_E4M3, d_w, d_scale, d_x, nullptr, d_y, M, N, K, false, st, pdl != 0);
 }
 
 size_t mc_sm100_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {
@@ -475,8 +518,10 @@ mc_status_t mc_sm100_gemm_bf16(void* stream, void* d_workspace, size_t ws_size, 
         }
         return MC_OK;
     }
-    return skinny_gemm(SKINNY_W_BF16, d_a, nullptr, (const uint16_t*)d_b, nullptr, (uint16_t*)d_c, M, N, K,
-                       d_workspace, ws_size, st, false);
+    (void)d_workspace;
+    (void)ws_size;
+    return skinny_gemm(SKINNY_W_BF16, d_a, nullptr, (const uint16_t*)d_b, nullptr, (uint16_t*)d_c, M, N, K, false, st,
+                       false);
 }
 
 mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N,
@@ -493,8 +538,10 @@ mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size,
         set_error("mc_sm100_gemm_fp8_q: shape N=%u K=%u not supported by the tcgen05 path", N, K);
         return MC_E_UNSUPPORTED;
     }
-    return skinny_gemm(SKINNY_W8A8, d_w_fp8, d_w_scale, (const uint16_t*)d_x_fp8, d_x_scale, d_y_bf16, M, N,
-                       K, d_workspace, ws_size, (cudaStream_t)stream, false);
+    (void)d_workspace;
+    (void)ws_size;
+    return skinny_gemm(SKINNY_W8A8, d_w_fp8, d_w_scale, (const uint16_t*)d_x_fp8, d_x_scale, d_y_bf16, M, N, K, false,
+                       (cudaStream_t)stream, false);
 }
 
 mc_status_t mc_sm100_quant_rows(const uint16_t* d_x, uint8_t* d_xq, float* d_scale, uint32_t M, uint32_t K,
@@ -538,6 +585,20 @@ mc_status_t mc_sm100_gemm_fp8(void* stream, void* d_workspace, size_t ws_size, u
     if (s != MC_OK) return s;
     return mc_sm100_gemm_fp8_q(stream, d_workspace, ws_size, M, N, K, d_w_fp8, d_w_scale, d_x_fp8_scratch,
                                d_x_scale_scratch, d_y_bf16);
+}
+
+mc_status_t mc_sm100_residual_rmsnorm_rows(uint16_t* d_res, const uint16_t* d_add, const uint16_t* d_norm_w,
+                                           uint16_t* d_out, uint32_t rows, uint32_t n, float eps, void* stream,
+                                           int32_t pdl) {
+    clear_error();
+    if (d_res == nullptr || d_norm_w == nullptr || d_out == nullptr || rows == 0 || n == 0) {
+        set_error("mc_sm100_residual_rmsnorm_rows: invalid args (rows=%u n=%u)", rows, n);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    (void)launch(residual_rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, pdl != 0, d_res, d_add,
+                 d_norm_w, d_out, n, eps);
+    MCL_CHECK_LAUNCH("residual_rmsnorm_rows");
+    return MC_OK;
 }
 
 // ---- greedy -------------------------------------------------------------------------

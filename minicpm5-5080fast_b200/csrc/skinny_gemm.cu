@@ -12,9 +12,12 @@
 // memory ring in the canonical K-major 128-byte-swizzled layout, converting e4m3
 // weights to bf16 on the way (weight-only form); warp 8 issues the MMAs and
 // commits each stage back to the producers; warps 0-3 then read the accumulator
-// with tcgen05.ld, apply the scales and store bf16 (or fp32 split-K partials that a
-// second kernel merges in fixed order).  No TMA tensor maps, no multicast, no
-// clusters.  Every wait is bounded; a wait that runs out raises a flag in global
+// with tcgen05.ld into shared memory.  Small N is split along K over a thread-block
+// cluster (up to 8 CTAs per row tile): after a cluster barrier every CTA sums its
+// slice of the tile over the cluster's partial accumulators through distributed
+// shared memory, in rank order (no atomics, no global scratch, bit-reproducible),
+// applies the scales (and the SwiGLU over interleaved gate/up rows when asked) and
+// stores bf16.  No TMA tensor maps, no multicast.  Every wait is bounded; a wait that runs out raises a flag in global
 // memory and all roles fall through to the common exit, where TMEM is released.
 #include "skinny_gemm.cuh"
 
@@ -97,10 +100,10 @@ struct SkinnyArgs {
     const float* w_scale;   // [N] or null
     const void* x;          // [M,K] bf16 (modes 0,1) or e4m3 (mode 2)
     const float* x_scale;   // [M] (mode 2) or null
-    uint16_t* y;            // [M,N] bf16
-    float* partial;         // [S,M,N] fp32 when splits > 1
+    uint16_t* y;            // [M,N] bf16 ([M,N/2] behind the SwiGLU epilogue)
     uint32_t M, N, K;
-    uint32_t splits, kb_per_split;
+    uint32_t splits, kb_per_split;   // splits = cluster size along x
+    uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
 };
 
 // swizzled byte offset of 16-byte chunk `cc` (0..7) of tile row `row`
@@ -271,17 +274,18 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
     }
 
     // ---------------------------------------------------------------------- epilogue
+    // (1) accumulator -> this CTA's shared memory, red[m][n_local] fp32 (the ring is free:
+    //     every MMA that read it has completed once accum_bar fires)
+    float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
     if (warp < 4) {
-        const bool ok = (kb1 > kb0) && mbar_wait(accum_bar, 0u, abortp);
+        const bool have = kb1 > kb0;
+        const bool ok = have && mbar_wait(accum_bar, 0u, abortp);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t n = n0 + warp * 32u + lane;
-        float ws = 1.0f;
-        if (a.partial == nullptr) {
-            if (a.w_scale != nullptr && n < a.N) ws = a.w_scale[n];
-        }
 #pragma unroll
         for (int c0 = 0; c0 < NPAD; c0 += 16) {
             uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
             if (ok) {
                 const uint32_t taddr = tmem_base + ((warp * 32u) << 16) + (uint32_t)c0;
                 asm volatile(
@@ -291,25 +295,68 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t m = c0 + j;
-                    if (m < a.M && n < a.N) {
-                        float v = __uint_as_float(r[j]);
-                        if constexpr (MODE == SKINNY_W_E4M3) v *= 7.205759403792794e16f;   // 2^56 = 2^120 / 2^64
-                        if (a.partial != nullptr) {
-                            a.partial[((size_t)split * a.M + m) * a.N + n] = v;
-                        } else {
-                            v *= ws;
-                            if (MODE == SKINNY_W8A8) v *= a.x_scale[m];
-                            a.y[(size_t)m * a.N + n] = f32_to_bf16_bits(v);
-                        }
-                    }
-                }
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) red[(c0 + j) * kTileN + warp * 32u + lane] = __uint_as_float(r[j]);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    // (2) every CTA of the cluster has published its partial tile
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    // (3) this CTA finishes a contiguous slice of the tile: fixed rank order over the cluster
+    {
+        const uint32_t S = a.splits, rank = split;
+        const uint32_t red_s = smem_u32(red);
+        const bool failed = *abortp != 0;
+        if (!a.swiglu) {
+            const uint32_t total = a.M * kTileN;
+            const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
+            for (uint32_t e = lo + tid; e < hi; e += kThreads) {
+                const uint32_t m = e / kTileN, nl = e % kTileN, n = n0 + nl;
+                float acc = 0.f;
+                for (uint32_t r = 0; r < S; ++r) {
+                    uint32_t ra;
+                    float v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 4u * e), "r"(r));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+                    acc += v;
+                }
+                if (n < a.N && !failed) {
+                    if constexpr (MODE == SKINNY_W_E4M3) acc *= 7.205759403792794e16f;   // 2^56 = 2^120 / 2^64
+                    if (a.w_scale != nullptr) acc *= a.w_scale[n];
+                    if (MODE == SKINNY_W8A8) acc *= a.x_scale[m];
+                    a.y[(size_t)m * a.N + n] = f32_to_bf16_bits(acc);
+                }
+            }
+        } else {
+            const uint32_t half = kTileN / 2, total = a.M * half;
+            const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
+            for (uint32_t e = lo + tid; e < hi; e += kThreads) {
+                const uint32_t m = e / half, p = e % half, n = n0 + 2u * p;
+                float gt = 0.f, up = 0.f;
+                for (uint32_t r = 0; r < S; ++r) {
+                    uint32_t ra;
+                    float2 v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 4u * (m * kTileN + 2u * p)), "r"(r));
+                    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(ra) : "memory");
+                    gt += v.x;
+                    up += v.y;
+                }
+                if (n + 1 < a.N && !failed) {
+                    if constexpr (MODE == SKINNY_W_E4M3) { gt *= 7.205759403792794e16f; up *= 7.205759403792794e16f; }
+                    if (a.w_scale != nullptr) { gt *= a.w_scale[n]; up *= a.w_scale[n + 1]; }
+                    if (MODE == SKINNY_W8A8) { gt *= a.x_scale[m]; up *= a.x_scale[m]; }
+                    const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(gt) << 16);
+                    const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
+                    a.y[(size_t)m * (a.N / 2u) + (n >> 1)] = f32_to_bf16_bits(swiglu_f32(gb, ub));
+                }
+            }
+        }
+    }
+    // (4) nobody leaves while a peer may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -317,43 +364,29 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
     }
 }
 
-// Fixed-order merge of the split-K partials, scales applied to the finished sum.
-__global__ void skinny_merge_kernel(const float* __restrict__ partial, const float* __restrict__ w_scale,
-                                    const float* __restrict__ x_scale, uint32_t S, uint32_t M, uint32_t N,
-                                    uint16_t* __restrict__ y) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= M * N) return;
-    float acc = 0.f;
-    for (uint32_t s = 0; s < S; ++s) acc += partial[(size_t)s * M * N + i];
-    if (w_scale != nullptr) acc *= w_scale[i % N];
-    if (x_scale != nullptr) acc *= x_scale[i / N];
-    y[i] = f32_to_bf16_bits(acc);
-}
-
 // ---- host side ---------------------------------------------------------------------------
 namespace {
 
 struct Plan { uint32_t tiles, splits, kb_per_split; };
 
+// Cluster size along K: the largest of 8/4/2/1 that keeps the grid within two CTAs
+// per SM and leaves every CTA at least two K blocks.
 Plan make_plan(uint32_t N, uint32_t K, uint32_t bk) {
     Plan p;
     p.tiles = (N + kTileN - 1) / kTileN;
     const uint32_t nkb = (K + bk - 1) / bk;
-    const uint32_t want = 2u * (uint32_t)sm_count();            // two CTAs per SM
-    uint32_t s = 1;
-    if (p.tiles < want) {
-        s = (want + p.tiles - 1) / p.tiles;
-        const uint32_t max_s = nkb / 4 ? nkb / 4 : 1;           // at least four K blocks per split
-        if (s > max_s) s = max_s;
-    }
+    const uint32_t room = 2u * (uint32_t)sm_count();
+    uint32_t s = 8;
+    while (s > 1 && (p.tiles * s > room || nkb / s < 2)) s >>= 1;
+    p.splits = s;
     p.kb_per_split = (nkb + s - 1) / s;
-    p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
     return p;
 }
 
 template <int MODE, int NPAD>
 mc_status_t launch_one(const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
     constexpr size_t smem = (size_t)kStages * (kTileN + NPAD) * kRowBytes + 1024;
+    static_assert((size_t)NPAD * kTileN * 4 <= (size_t)kStages * (kTileN + NPAD) * kRowBytes, "reduce tile must fit in the ring");
     auto kern = skinny_gemm_kernel<MODE, NPAD>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -364,7 +397,21 @@ mc_status_t launch_one(const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, 
         }
         attr_done = true;
     }
-    (void)launch(kern, dim3(grid), dim3(kThreads), smem, stream, pdl, a);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = a.splits;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 2 : 1;
+    (void)cudaLaunchKernelEx(&cfg, kern, a);
     MCL_CHECK_LAUNCH("skinny_gemm");
     return MC_OK;
 }
@@ -382,42 +429,23 @@ bool skinny_shape_ok(uint32_t N, uint32_t K, int wb) {
     return N > 0 && K > 0 && (K % (wb == 2 ? 8u : 16u)) == 0;
 }
 
-size_t skinny_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {
-    if (M <= 4 || M > 64) return 0;
-    const Plan p64 = make_plan(N, K, 64), p128 = make_plan(N, K, 128);
-    const uint32_t s = p64.splits > p128.splits ? p64.splits : p128.splits;
-    return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
-}
+// Split-K partials travel through distributed shared memory: no global workspace.
+size_t skinny_workspace_bytes(uint32_t, uint32_t, uint32_t) { return 0; }
 
 mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uint16_t* x, const float* x_scale,
-                        uint16_t* y, uint32_t M, uint32_t N, uint32_t K, void* workspace, size_t ws_size,
-                        cudaStream_t stream, bool pdl) {
-    if (M == 0 || M > 64 || !aligned16(w) || !aligned16(x)) {
+                        uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu, cudaStream_t stream, bool pdl) {
+    if (M == 0 || M > 64 || !aligned16(w) || !aligned16(x) || (swiglu && (N & 1u))) {
         set_error("skinny_gemm: invalid args (M=%u N=%u K=%u)", M, N, K);
         return MC_E_INVALID_ARGUMENT;
     }
-    Plan p = make_plan(N, K, mode == SKINNY_W8A8 ? 128u : 64u);
-    if (p.splits > 1 && (workspace == nullptr || ws_size < (size_t)p.splits * M * N * sizeof(float))) {
-        // no room for partials: one CTA walks the whole K of its tile (fewer CTAs, same result)
-        p.splits = 1;
-        p.kb_per_split = (K + (mode == SKINNY_W8A8 ? 127u : 63u)) / (mode == SKINNY_W8A8 ? 128u : 64u);
-    }
+    const Plan p = make_plan(N, K, mode == SKINNY_W8A8 ? 128u : 64u);
     SkinnyArgs a{};
     a.w = w; a.w_scale = w_scale; a.x = x; a.x_scale = x_scale; a.y = y;
-    a.partial = p.splits > 1 ? reinterpret_cast<float*>(workspace) : nullptr;
-    a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.kb_per_split = p.kb_per_split;
+    a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.kb_per_split = p.kb_per_split; a.swiglu = swiglu ? 1u : 0u;
     const uint32_t grid = p.tiles * p.splits;
-    mc_status_t s;
-    if (mode == SKINNY_W_BF16) s = launch_mode<SKINNY_W_BF16>(a, grid, stream, pdl);
-    else if (mode == SKINNY_W_E4M3) s = launch_mode<SKINNY_W_E4M3>(a, grid, stream, pdl);
-    else s = launch_mode<SKINNY_W8A8>(a, grid, stream, pdl);
-    if (s != MC_OK) return s;
-    if (p.splits > 1) {
-        skinny_merge_kernel<<<dim3((M * N + 255u) / 256u), dim3(256), 0, stream>>>(a.partial, w_scale, x_scale, p.splits,
-                                                                                  M, N, y);
-        MCL_CHECK_LAUNCH("skinny_merge");
-    }
-    return MC_OK;
+    if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(a, grid, stream, pdl);
+    if (mode == SKINNY_W_E4M3) return launch_mode<SKINNY_W_E4M3>(a, grid, stream, pdl);
+    return launch_mode<SKINNY_W8A8>(a, grid, stream, pdl);
 }
 
 // 1 when a bounded wait of the tensor-core kernel ran out since the last call (and clears it).

@@ -42,7 +42,7 @@ def run_fp8(pkg, g, q, sc, x, pdl=False):
 # ---- M = 1 bf16 ----------------------------------------------------------------------
 @pytest.mark.parametrize("N,K", [(1, 8), (7, 64), (17, 104), (8, 2048), (255, 2304), (2560, 2048), (2048, 6144),
                                  (1000, 8192), (QKV_B, K_B), (K_B, K_B), (K_B, I_B)])
-@pytest.mark.parametrize("math", [0, 1])
+@pytest.mark.parametrize("math", [0, 1, 2])
 def test_decode_gemv_rows(pkg, g, N, K, math):
     pkg.debug_set_math(math, -1)
     w = onp.seeded_bf16(1000 + N + K, (N, K), 0.02)
@@ -51,7 +51,7 @@ def test_decode_gemv_rows(pkg, g, N, K, math):
     check_close(got, onp.linear_bf16(w, x), what=f"rows N={N} K={K}")
     got2 = run_bf16(pkg, g, w, x, pdl=True)
     assert np.array_equal(got, got2), "PDL launch must give identical bits"
-    pkg.debug_set_math(1, -1)
+    pkg.debug_set_math(2, -1)
 
 
 def test_math_forms_bit_identical(pkg, g):
@@ -63,6 +63,7 @@ def test_math_forms_bit_identical(pkg, g):
     pkg.debug_set_math(1, 1)
     assert np.array_equal(a, run_bf16(pkg, g, w, x))
     assert np.array_equal(b, run_fp8(pkg, g, q, sc, x))
+    pkg.debug_set_math(2, 2)
 
 
 @pytest.mark.parametrize("N,K,S", [(64, 256, 2), (2048, 2048, 8), (K_B, K_B, 4), (K_B, I_B, 8), (QKV_B, K_B, 2)])
@@ -83,7 +84,7 @@ def test_baseline_config1_against_reference_fixture(pkg, g, golden):
 # ---- M = 1 fp8 -------------------------------------------------------------------------
 @pytest.mark.parametrize("N,K", [(1, 16), (8, 2048), (24, 2048), (255, 2048), (2560, 2048), (2048, 6144),
                                  (1000, 8192), (64, 100), (33, 2056), (2 * I_B, K_B), (K_B, I_B)])
-@pytest.mark.parametrize("math", [0, 1])
+@pytest.mark.parametrize("math", [0, 1, 2])
 def test_gemv_fp8(pkg, g, N, K, math):
     pkg.debug_set_math(-1, math)
     w = onp.seeded_bf16(5000 + N + K, (N, K), 0.02)
@@ -92,10 +93,10 @@ def test_gemv_fp8(pkg, g, N, K, math):
     got = run_fp8(pkg, g, q, sc, x)
     check_close(got, onp.linear_fp8(q, sc, x), abs_floor=1e-4, what=f"fp8 N={N} K={K}")
     assert np.array_equal(got, run_fp8(pkg, g, q, sc, x, pdl=True))
-    pkg.debug_set_math(-1, 1)
+    pkg.debug_set_math(-1, 2)
 
 
-@pytest.mark.parametrize("math", [0, 1])
+@pytest.mark.parametrize("math", [0, 1, 2])
 def test_gemv_fp8_whole_code_space(pkg, g, math):
     """Every byte value as a weight (subnormals, negative zero, the two NaN
     codes that decode to +/-480), scales in [1e-3, 1], x in [-1.5, 1.5]: the
@@ -109,7 +110,7 @@ def test_gemv_fp8_whole_code_space(pkg, g, math):
     x = onp.f32_to_bf16(rng.uniform(-1.5, 1.5, K).astype(np.float32))
     ref = onp.f32_to_bf16(onp.linear_f64(onp.e4m3_to_f32(q), x, sc))
     check_close(run_fp8(pkg, g, q, sc, x), ref, abs_floor=1e-4, what="fp8 all codes")
-    pkg.debug_set_math(-1, 1)
+    pkg.debug_set_math(-1, 2)
 
 
 # ---- fused variants ----------------------------------------------------------------------
@@ -229,9 +230,11 @@ def test_gemv_fp8_rows_m(pkg, g, golden, M, N, K):
     check_close(got, onp.linear_fp8(q, sc, X), abs_floor=1e-4, what=f"fp8 rows_m M={M} N={N} K={K}")
     if base and f"c3_y_fp8_m{M}" in golden["baseline"]:
         check_close(got, golden["baseline"][f"c3_y_fp8_m{M}"], abs_floor=1e-4, what=f"config3 fp8 M={M} vs reference")
-    if M <= 4:   # CUDA-core rows: each row bit-equal to the M=1 call (the reference's anchor, gemv_fp8.cu:533-607)
+    if M <= 4:   # CUDA-core rows: each row bit-equal to the M=1 call of the same kernel form
+        pkg.debug_set_math(-1, 1)                 # (the reference's anchor, gemv_fp8.cu:533-607)
         for m in range(M):
             assert np.array_equal(got[m], run_fp8(pkg, g, q, sc, X[m])), f"row {m} differs from the solo call"
+        pkg.debug_set_math(-1, 2)
 
 
 # ---- greedy ---------------------------------------------------------------------------------
@@ -379,3 +382,43 @@ def test_gemm_without_workspace_still_correct(pkg, g):
 def test_no_bounded_wait_ran_out(pkg, g):
     g.sync()
     assert pkg.debug_take_error() == 0
+
+
+# ---- decode-chain kernel: the exact-path fallbacks ---------------------------------------------
+@pytest.mark.parametrize("case", ["tiny", "huge", "nan_code", "inf"])
+def test_gemv_fp8_fast_form_fallbacks(pkg, g, case):
+    """The f16 staging of x is only used when it is exact; activations outside the
+    f16 range (after the 2^6 scaling) and rows holding the two NaN codes take the
+    bit-placement path.  Results must not depend on which path ran."""
+    pkg.debug_set_math(-1, 2)
+    N, K = 300, 2304
+    w = onp.seeded_bf16(170, (N, K), 0.02)
+    q, sc = onp.make_fp8_weight(w)
+    x = onp.seeded_bf16(171, (K,), 1.0)
+    if case == "tiny":
+        x[5] = onp.f32_to_bf16(np.array([3e-9], np.float32))[0]       # below the exact f16 range
+    elif case == "huge":
+        x[7] = onp.f32_to_bf16(np.array([4000.0], np.float32))[0]     # 4000 * 64 overflows f16
+    elif case == "nan_code":
+        q = q.copy(); q[11, 100] = 0x7F; q[12, 7] = 0xFF              # decode to +/-480 in the reference
+    elif case == "inf":
+        x[9] = 0x7F80
+    ref32 = onp.linear_f64(onp.e4m3_to_f32(q), x, sc)
+    got = run_fp8(pkg, g, q, sc, x)
+    if case == "inf":
+        assert np.array_equal(np.isfinite(onp.bf16_to_f32(got)), np.isfinite(ref32))
+    else:
+        check_close(got, onp.f32_to_bf16(ref32), abs_floor=1e-4, what=f"fast fp8 {case}")
+
+
+def test_residual_rmsnorm_rows(pkg, g):
+    rows, n = 5, 2304
+    res = onp.seeded_bf16(180, (rows, n), 1.2)
+    add = onp.seeded_bf16(181, (rows, n), 0.6)
+    nw = onp.seeded_bf16(182, (n,), 1.0)
+    dres, dout = g.dev(res), g.empty_u16(rows, n)
+    pkg.launch_residual_rmsnorm_rows(dres, g.dev(add), g.dev(nw), dout, rows, n, 1e-6)
+    g.sync()
+    want_res = onp.add_bf16(res, add)
+    assert np.array_equal(g.host_u16(dres), want_res)
+    check_close(g.host_u16(dout), onp.rmsnorm_bf16(nw, want_res), what="residual_rmsnorm_rows")
