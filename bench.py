@@ -232,6 +232,26 @@ class Stream:
         g = torch.Generator(device=dev)
         g.manual_seed(20260908 + 5000)            # same seed on every rank: shards of one logical model
         self.layers = []
+        self.handle = None
+        self.desc = None
+        if world == 1:
+            # one GPU: the weights live in the library's own arena layout and the step is the
+            # library's decode-stack object (C ABI); the per-call launch sequence below is kept
+            # for the sharded runs
+            self.desc = pkg.stack_desc(L, H, QKV, I, V, fp8=self.fp8, max_batch=max(m, 1), graph=True)
+            wbytes, sbytes = pkg.stack_sizes(self.desc)
+            self.arena = torch.zeros(wbytes, dtype=torch.uint8, device=dev)
+            self.scratch = torch.zeros(sbytes, dtype=torch.uint8, device=dev)
+
+        def place(layer, name, t):
+            """Copies a generated tensor to its arena section and returns a view of it there."""
+            if self.desc is None or t is None:
+                return t
+            off, n = pkg.stack_section(self.desc, layer, name)
+            flat = t.contiguous().view(torch.uint8).reshape(-1)
+            assert flat.numel() == n, (name, flat.numel(), n)
+            self.arena[off:off + n].copy_(flat)
+            return self.arena[off:off + n].view(t.dtype).view(t.shape)
 
         def bf16_bits(t):
             return t.to(torch.bfloat16).view(torch.int16)
@@ -252,19 +272,25 @@ class Stream:
             q = (w / sc[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
             return q, sc.contiguous()
 
-        for _ in range(L):
+        def placed(li, name, ws):
+            w, sc = ws
+            return place(li, name, w), place(li, name + "_scale", sc)
+
+        for li in range(L):
             lay = {}
-            lo, hi, _ = shard_rows(QKV, world, rank); lay["qkv"] = make(QKV, H, lo, hi)
-            lo, hi, _ = shard_rows(H, world, rank); lay["o"] = make(H, H, lo, hi)
-            lo, hi, _ = shard_rows(I, world, rank); lay["gu"] = make(2 * I, H, lo, hi, pairs=True)
-            lo, hi, _ = shard_rows(H, world, rank); lay["down"] = make(H, I, lo, hi)
-            lay["n1"] = bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev))
-            lay["n2"] = bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev))
+            lo, hi, _ = shard_rows(QKV, world, rank); lay["qkv"] = placed(li, "qkv", make(QKV, H, lo, hi))
+            lo, hi, _ = shard_rows(H, world, rank); lay["o"] = placed(li, "o", make(H, H, lo, hi))
+            lo, hi, _ = shard_rows(I, world, rank); lay["gu"] = placed(li, "gate_up", make(2 * I, H, lo, hi, pairs=True))
+            lo, hi, _ = shard_rows(H, world, rank); lay["down"] = placed(li, "down", make(H, I, lo, hi))
+            lay["n1"] = place(li, "norm1", bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev)))
+            lay["n2"] = place(li, "norm2", bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev)))
             self.layers.append(lay)
         lo, hi, per = shard_rows(V, world, rank)
         self.v_lo, self.v_rows, self.v_per = lo, hi - lo, per
-        self.lm = make(V, H, lo, hi)
-        self.nf = bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev))
+        self.lm = placed(0, "lm_head", make(V, H, lo, hi))
+        self.nf = place(0, "final_norm", bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev)))
+        if self.desc is not None:
+            self.handle = pkg.stack_create(self.desc, self.arena, self.scratch)
         z = lambda *s: torch.zeros(s, dtype=torch.int16, device=dev)
         self.per = {"qkv": shard_rows(QKV, world, 0)[2], "o": shard_rows(H, world, 0)[2],
                     "mid": shard_rows(I, world, 0)[2], "down": shard_rows(H, world, 0)[2]}
@@ -281,15 +307,70 @@ class Stream:
         self.pair = torch.zeros((world, m, 2), dtype=torch.float32, device=dev)
         self.launches = 0
         if m != 1:
-            raise SystemExit("bench: the stream workload currently runs with M=1")
+            if world != 1:
+                raise SystemExit("bench: the batched (M > 1) stream runs on one GPU")
+            if m > 64:
+                raise SystemExit("bench: M <= 64")
+            self.h = z(m, H)
+            self.ctx = z(m, H)
+            self.qkv_m, self.o_m, self.mid_m, self.dn_m = z(m, QKV), z(m, H), z(m, I), z(m, H)
+            self.logits = z(m, V)
 
     def gather(self, full, shard):
         if self.world > 1:
-            self.dist.all_gather_into_tensor(full.view(-1), shard.view(-1))
+            # NCCL has no 16-bit integer type: the same bits travel as bf16
+            self.dist.all_gather_into_tensor(full.view(-1).view(self.torch.bfloat16), shard.view(-1).view(self.torch.bfloat16))
             return full.view(-1)
         return shard.view(-1)
 
+    def step_batched(self, pdl=True):
+        """M > 1: the reference's BatchGroup sequence (native/runtime/batch_group.cpp:745-807):
+        separate residual+RMSNorm kernels between the batched GEMMs."""
+        p, fp8, m = self.pkg, self.fp8, self.m
+        res = self.res[0]
+        res.copy_(self.x_in)
+        addend, n = None, 0
+
+        def linear(ws, x, y, N, K):
+            w, s = ws
+            if fp8:
+                p.launch_gemv_fp8_rows_m(w, s, x, y, m, N, K, pdl=pdl)
+            else:
+                p.gemm_bf16(None, None, 0, m, N, K, w, x, y)
+
+        for lay in self.layers:
+            p.launch_residual_rmsnorm_rows(res, addend, lay["n1"], self.h, m, H, 1e-6, pdl=pdl)
+            linear(lay["qkv"], self.h, self.qkv_m, QKV, H)
+            self.ctx.copy_(self.qkv_m[:, :H])            # stand-in for attention (not a kernel of this library)
+            linear(lay["o"], self.ctx, self.o_m, H, H)
+            p.launch_residual_rmsnorm_rows(res, self.o_m, lay["n2"], self.h, m, H, 1e-6, pdl=pdl)
+            w, s = lay["gu"]
+            p.launch_gate_up_swiglu(w, s, self.h, self.mid_m, m, 2 * I, H, pdl=pdl)
+            linear(lay["down"], self.mid_m, self.dn_m, H, I)
+            addend = self.dn_m
+            n += 6
+        p.launch_residual_rmsnorm_rows(res, addend, self.nf, self.h, m, H, 1e-6, pdl=pdl)
+        w, s = self.lm
+        if m <= 8:
+            p.launch_lm_head_argmax(w, s, self.h, self.logits, V, m, V, H, 0, self.stage, self.tok, self.val, pdl=pdl)
+        else:
+            linear(self.lm, self.h, self.logits, V, H)
+            p.launch_argmax_bf16(self.logits, m, V, V, 0, self.stage, self.tok, self.val, pdl=pdl)
+        self.launches = n + 4
+        return self.tok
+
+    def step_stack(self):
+        """One GPU: the whole step through the C ABI's decode-stack object."""
+        m = self.m
+        self.pkg.stack_step(self.handle, self.x_in, m, self.tok)
+        self.launches = (4 * L + 2) if m == 1 else (6 * L + 1 + (2 if m <= 4 else 3))
+        return self.tok
+
     def step(self, pdl=True):
+        if self.handle is not None:
+            return self.step_stack()
+        if self.m != 1:
+            return self.step_batched(pdl)
         p, fp8 = self.pkg, self.fp8
         ra, rb = self.res                    # residual ping-pong: qkv reads ra -> writes rb, gate_up reads rb -> writes ra
         addend = None
@@ -440,16 +521,23 @@ def run_ours(args):
         res_dev = st.y if single else st.tok
         hx = torch.randn(tuple(x_dev.shape)).to(torch.bfloat16).view(torch.int16).pin_memory()
         hres = torch.zeros(tuple(res_dev.shape), dtype=res_dev.dtype).pin_memory()
+        if not single and st.handle is not None:
+            # the user-facing call: host activations in, host tokens out, one C-ABI call per step
+            def e2e_step():
+                pkg.stack_step_host(st.handle, hx, args.m, hres, stream)
+        else:
+            def e2e_step():
+                x_dev.copy_(hx, non_blocking=True)
+                run()
+                hres.copy_(res_dev, non_blocking=True)
+                stream.synchronize()
         for _ in range(3):
-            x_dev.copy_(hx, non_blocking=True); run(); hres.copy_(res_dev, non_blocking=True); stream.synchronize()
+            e2e_step()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(stream)
         for _ in range(args.steps):
-            x_dev.copy_(hx, non_blocking=True)
-            run()
-            hres.copy_(res_dev, non_blocking=True)
-            stream.synchronize()
+            e2e_step()
         e1.record(stream)
         barrier()
         ms_e2e = e0.elapsed_time(e1)
@@ -490,9 +578,16 @@ def run_ours(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        # A captured graph that holds NCCL work makes the communicator teardown block on this
+        # stack: release the graph, meet once more, and leave without the teardown.
+        del run
+        graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():

@@ -281,6 +281,89 @@ MC_SM100_API mc_status_t mc_sm100_linear_host(int32_t kind, const void* d_w, con
                                  uint32_t K, uint16_t* d_x_stage, uint16_t* d_y_stage,
                                  void* d_workspace, size_t ws_size, void* stream);
 
+/* ------------------------------------------------------------ decode stack --- */
+
+/* The linear layers of a whole decode step as one object: weight-arena layout,
+ * per-layer dispatch and CUDA-graph replay -- the part of the reference's
+ * executors that belongs to this path (run_real_forward's linear dispatch,
+ * native/runtime/forward.cpp:98-160, 206-237, 306-373, 443-462; mc_batch_step's GEMM
+ * sequence, native/runtime/batch_group.cpp:745-807; section placement,
+ * native/runtime/weight_loader.cpp:355-365, 563-630; capture and replay,
+ * native/runtime/decode_executor.cpp:163-209).  Attention is stood in for by the
+ * first `hidden` features of the fused qkv output.  Per layer:
+ *   h = rmsnorm1(x) ; qkv = Wqkv h ; x += Wo qkv[:hidden] ; h = rmsnorm2(x) ;
+ *   x += Wdown swiglu(Wgate_up h)      and finally  token = argmax(Wlm rmsnorm_f(x)). */
+typedef struct mc_sm100_stack_desc_t {
+    uint32_t struct_size;        /* caller sets sizeof(mc_sm100_stack_desc_t) */
+    uint32_t layers, hidden, qkv_rows, inter, vocab;
+    uint32_t precision;          /* 0 = bf16, 2 = e4m3 weight-only (values of mc_precision_t) */
+    uint32_t max_batch;          /* 1..64 */
+    float    eps;
+    uint32_t enable_cuda_graph;
+    uint32_t reserved[4];        /* must be zero */
+} mc_sm100_stack_desc_t;
+
+typedef struct mc_sm100_stack* mc_sm100_stack_t;
+
+/* Sections of the weight arena (each 256-byte aligned, compact, layer-major):
+ * 0 qkv, 1 o, 2 gate_up (rows INTERLEAVED gate_j, up_j), 3 down, 4 norm1, 5 norm2,
+ * 6..9 fp32 row scales of 0..3 (e4m3 only; gate_up scales interleaved too),
+ * 10 lm_head, 11 final_norm, 12 lm_head scales (layer ignored for 10..12). */
+MC_SM100_API mc_status_t mc_sm100_stack_sizes(const mc_sm100_stack_desc_t* desc, uint64_t* weight_bytes,
+                                              uint64_t* scratch_bytes);
+MC_SM100_API mc_status_t mc_sm100_stack_section(const mc_sm100_stack_desc_t* desc, uint32_t layer,
+                                                uint32_t which, uint64_t* offset, uint64_t* bytes);
+
+/* The caller owns both arenas (device memory, 256-byte aligned, sizes from
+ * mc_sm100_stack_sizes) and fills the weight arena at the section offsets; the
+ * object itself allocates no device memory. */
+MC_SM100_API mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_weights,
+                                               void* d_scratch, mc_sm100_stack_t* out);
+MC_SM100_API void mc_sm100_stack_destroy(mc_sm100_stack_t stack);
+
+/* One step on device buffers: x [M, hidden] bf16 -> greedy tokens [M]; stream-ordered,
+ * no synchronisation (capturable). */
+MC_SM100_API mc_status_t mc_sm100_stack_step(mc_sm100_stack_t stack, const uint16_t* d_x, uint32_t M,
+                                             int32_t* d_tokens, void* stream);
+
+/* Device pointer to the bf16 logits [M, vocab] the last step wrote (inside the scratch arena). */
+MC_SM100_API const uint16_t* mc_sm100_stack_logits(mc_sm100_stack_t stack);
+
+/* One step on HOST buffers: H2D of x, the step (a CUDA graph captured on first use
+ * per batch size when enabled and `stream` is not the default stream, else eager
+ * launches of the same kernels), D2H of the tokens, one stream synchronise -- the shape
+ * of mc_decode_one / mc_batch_step around a step. */
+MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const uint16_t* h_x, uint32_t M,
+                                                  int32_t* h_tokens, void* stream);
+
+/* ------------------------------------------------------------ packed weights --- */
+
+/* Reader of the reference's packed weight file (WPK v1: tools/minicpm_common.py:47-75,
+ * 318-348) and loader into this library's arena layout; stands for
+ * WeightLoader::load_wpk / load_wpk_fp8 (native/runtime/weight_loader.cpp:195-726) on
+ * this path.  Files packed for target_sm 120 are accepted as they are. */
+typedef struct mc_sm100_wpk* mc_sm100_wpk_t;
+typedef struct mc_sm100_wpk_section_t {
+    uint64_t name_hash;          /* FNV-1a 64 of the section name */
+    uint32_t dtype, layout, rank;/* dtype 0 = bf16, 2 = e4m3 + fp32 row scales */
+    uint32_t dims[8];
+    uint64_t data_offset, data_bytes, scale_offset, scale_bytes;
+} mc_sm100_wpk_section_t;
+
+MC_SM100_API uint64_t mc_sm100_wpk_name_hash(const char* name);
+/* Opens and validates header and TOC (MC_E_IO / MC_E_MODEL_MISMATCH with a message). */
+MC_SM100_API mc_status_t mc_sm100_wpk_open(const char* path, mc_sm100_wpk_t* out);
+MC_SM100_API void mc_sm100_wpk_close(mc_sm100_wpk_t wpk);
+MC_SM100_API uint32_t mc_sm100_wpk_section_count(mc_sm100_wpk_t wpk);
+MC_SM100_API mc_status_t mc_sm100_wpk_find(mc_sm100_wpk_t wpk, const char* name, mc_sm100_wpk_section_t* out);
+/* Uploads rows [row_lo, row_hi) of a section (an N-shard) to device memory; with
+ * interleave != 0 the section is a fused gate|up tensor, the range counts (gate_j, up_j)
+ * pairs and the rows arrive interleaved (the layout mc_sm100_gate_up_swiglu reads).
+ * e4m3 sections also deliver their row scales to d_scale.  Synchronous (load time). */
+MC_SM100_API mc_status_t mc_sm100_wpk_upload(mc_sm100_wpk_t wpk, const char* name, uint32_t row_lo,
+                                             uint32_t row_hi, int32_t interleave, void* d_data,
+                                             uint64_t data_capacity, float* d_scale, void* stream);
+
 /* ---------------------------------------------------------------- debug hook -- */
 
 /* Not part of the frozen surface (same standing as the reference's

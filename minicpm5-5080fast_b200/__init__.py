@@ -58,6 +58,19 @@ SIGNATURES = {
     "mc_sm100_lm_head_argmax_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _i32,
                                                 _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_linear_host": (_i32, [_i32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "mc_sm100_stack_sizes": (_i32, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "mc_sm100_stack_section": (_i32, [_vp, _u32, _u32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "mc_sm100_stack_create": (_i32, [_vp, _vp, _vp, C.POINTER(_vp)]),
+    "mc_sm100_stack_destroy": (None, [_vp]),
+    "mc_sm100_stack_logits": (_vp, [_vp]),
+    "mc_sm100_stack_step": (_i32, [_vp, _vp, _u32, _vp, _vp]),
+    "mc_sm100_stack_step_host": (_i32, [_vp, _vp, _u32, _vp, _vp]),
+    "mc_sm100_wpk_name_hash": (C.c_uint64, [C.c_char_p]),
+    "mc_sm100_wpk_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
+    "mc_sm100_wpk_close": (None, [_vp]),
+    "mc_sm100_wpk_section_count": (_u32, [_vp]),
+    "mc_sm100_wpk_find": (_i32, [_vp, C.c_char_p, _vp]),
+    "mc_sm100_wpk_upload": (_i32, [_vp, C.c_char_p, _u32, _u32, _i32, _vp, C.c_uint64, _vp, _vp]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -231,3 +244,85 @@ def debug_set_math(bf16_math=-1, fp8_math=-1):
 
 def debug_take_error() -> int:
     return lib().mc_sm100_debug_take_error()
+
+
+# ---- decode stack ---------------------------------------------------------------------------
+class StackDesc(C.Structure):
+    _fields_ = [("struct_size", _u32), ("layers", _u32), ("hidden", _u32), ("qkv_rows", _u32), ("inter", _u32),
+                ("vocab", _u32), ("precision", _u32), ("max_batch", _u32), ("eps", C.c_float),
+                ("enable_cuda_graph", _u32), ("reserved", _u32 * 4)]
+
+
+SEC = {"qkv": 0, "o": 1, "gate_up": 2, "down": 3, "norm1": 4, "norm2": 5, "qkv_scale": 6, "o_scale": 7,
+       "gate_up_scale": 8, "down_scale": 9, "lm_head": 10, "final_norm": 11, "lm_head_scale": 12}
+
+
+def stack_desc(layers, hidden, qkv_rows, inter, vocab, fp8=False, max_batch=1, eps=1e-6, graph=True) -> StackDesc:
+    d = StackDesc()
+    d.struct_size = C.sizeof(StackDesc)
+    d.layers, d.hidden, d.qkv_rows, d.inter, d.vocab = layers, hidden, qkv_rows, inter, vocab
+    d.precision, d.max_batch, d.eps, d.enable_cuda_graph = (2 if fp8 else 0), max_batch, eps, int(graph)
+    return d
+
+
+def stack_sizes(desc):
+    w, s = C.c_uint64(), C.c_uint64()
+    _check(lib().mc_sm100_stack_sizes(C.byref(desc), C.byref(w), C.byref(s)))
+    return w.value, s.value
+
+
+def stack_section(desc, layer, which):
+    off, n = C.c_uint64(), C.c_uint64()
+    _check(lib().mc_sm100_stack_section(C.byref(desc), layer, SEC[which] if isinstance(which, str) else which,
+                                        C.byref(off), C.byref(n)))
+    return off.value, n.value
+
+
+def stack_create(desc, weights, scratch):
+    h = _vp()
+    _check(lib().mc_sm100_stack_create(C.byref(desc), _p(weights), _p(scratch), C.byref(h)))
+    return h
+
+
+def stack_destroy(handle):
+    lib().mc_sm100_stack_destroy(handle)
+
+
+def stack_step(handle, x, M, tokens, stream=None):
+    _check(lib().mc_sm100_stack_step(handle, _p(x), M, _p(tokens), _stream(stream)))
+
+
+def stack_step_host(handle, h_x, M, h_tokens, stream=None):
+    _check(lib().mc_sm100_stack_step_host(handle, _p(h_x), M, _p(h_tokens), _stream(stream)))
+
+
+def stack_logits_ptr(handle) -> int:
+    return lib().mc_sm100_stack_logits(handle)
+
+
+# ---- packed weight file -----------------------------------------------------------------------
+class WpkSection(C.Structure):
+    _fields_ = [("name_hash", C.c_uint64), ("dtype", _u32), ("layout", _u32), ("rank", _u32), ("dims", _u32 * 8),
+                ("data_offset", C.c_uint64), ("data_bytes", C.c_uint64), ("scale_offset", C.c_uint64),
+                ("scale_bytes", C.c_uint64)]
+
+
+def wpk_open(path: str):
+    h = _vp()
+    _check(lib().mc_sm100_wpk_open(path.encode(), C.byref(h)))
+    return h
+
+
+def wpk_close(h):
+    lib().mc_sm100_wpk_close(h)
+
+
+def wpk_find(h, name: str) -> WpkSection:
+    sec = WpkSection()
+    _check(lib().mc_sm100_wpk_find(h, name.encode(), C.byref(sec)))
+    return sec
+
+
+def wpk_upload(h, name, row_lo, row_hi, interleave, dst, scale_dst=None, stream=None):
+    _check(lib().mc_sm100_wpk_upload(h, name.encode(), row_lo, row_hi, int(interleave), _p(dst),
+                                     dst.numel() * dst.element_size(), _p(scale_dst), _stream(stream)))

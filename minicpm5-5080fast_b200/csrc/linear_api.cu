@@ -520,8 +520,10 @@ mc_status_t mc_sm100_gemm_bf16(void* stream, void* d_workspace, size_t ws_size, 
     }
     (void)d_workspace;
     (void)ws_size;
+    // launched with the programmatic-dependent-launch attribute: the kernel prefetches only
+    // weights before griddepcontrol.wait, so this is equivalent to plain stream order
     return skinny_gemm(SKINNY_W_BF16, d_a, nullptr, (const uint16_t*)d_b, nullptr, (uint16_t*)d_c, M, N, K, false, st,
-                       false);
+                       true);
 }
 
 mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N,
@@ -541,7 +543,7 @@ mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size,
     (void)d_workspace;
     (void)ws_size;
     return skinny_gemm(SKINNY_W8A8, d_w_fp8, d_w_scale, (const uint16_t*)d_x_fp8, d_x_scale, d_y_bf16, M, N, K, false,
-                       (cudaStream_t)stream, false);
+                       (cudaStream_t)stream, true);
 }
 
 mc_status_t mc_sm100_quant_rows(const uint16_t* d_x, uint8_t* d_xq, float* d_scale, uint32_t M, uint32_t K,

@@ -7,32 +7,36 @@
 // 16..64 TMEM columns.  The kernel is still bandwidth-bound (W is streamed once);
 // the tensor core only removes the per-row FMA cost that caps the CUDA-core family.
 //
-// One CTA = one (row tile, K split) work item; two CTAs fit per SM.  Warps 0-7
-// stream W (and the matching X slice) from global memory into a 4-stage shared
-// memory ring in the canonical K-major 128-byte-swizzled layout, converting e4m3
-// weights to bf16 on the way (weight-only form); warp 8 issues the MMAs and
-// commits each stage back to the producers; warps 0-3 then read the accumulator
-// with tcgen05.ld into shared memory.  Small N is split along K over a thread-block
-// cluster (up to 8 CTAs per row tile): after a cluster barrier every CTA sums its
-// slice of the tile over the cluster's partial accumulators through distributed
-// shared memory, in rank order (no atomics, no global scratch, bit-reproducible),
-// applies the scales (and the SwiGLU over interleaved gate/up rows when asked) and
-// stores bf16.  No TMA tensor maps, no multicast.  Every wait is bounded; a wait that runs out raises a flag in global
-// memory and all roles fall through to the common exit, where TMEM is released.
+// Two CTAs per SM, one (row tile, K slice) work item per CTA.
+//   warp 0   : TMA producer.  2-D tiled cp.async.bulk.tensor loads (no multicast) of
+//              the W tile [128 x BK] and the X tile [Mpad x BK] into a ring of
+//              128-byte-swizzled stages, completion on mbarriers.  The W loads of
+//              the first ring-full go out before griddepcontrol.wait.
+//   warp 1   : MMA issuer (one elected lane): tcgen05.mma per 32-byte K step,
+//              tcgen05.commit hands each stage back to the producer.
+//   warps 2-9: e4m3 weight-only form only: read the raw e4m3 tile that TMA landed,
+//              widen it to bf16 (exact) into the operand ring; idle otherwise.
+//   warps 2-5: epilogue: tcgen05.ld the accumulator into shared memory.
+// Small N is split along K over a thread-block cluster (up to 8 CTAs per row tile):
+// after a cluster barrier every CTA sums its slice of the tile over the cluster's
+// partial accumulators through distributed shared memory in rank order (no atomics,
+// no global scratch, bit-reproducible), applies the scales (and the SwiGLU over
+// interleaved gate/up rows when asked) and stores bf16.
+// Every wait is bounded; a wait that runs out raises a flag in global memory and all
+// roles fall through to the common exit, where TMEM is released.
 #include "skinny_gemm.cuh"
 
-#include <atomic>
+#include <cuda.h>
 
 namespace mcl {
 
 namespace {
 
 constexpr int kTileN = 128;        // weight rows per CTA (MMA M)
-constexpr int kStages = 4;
-constexpr int kProducerThreads = 256;
-constexpr int kThreads = kProducerThreads + 32;
-constexpr int kRowBytes = 128;     // shared-memory bytes per tile row (one swizzle atom row)
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kThreads = 320;      // 10 warps
+constexpr int kConvThreads = 256;  // warps 2..9
+constexpr int kRowBytes = 128;     // bytes per operand-tile row in shared memory (one swizzle row)
+constexpr unsigned long long kWaitLimitNs = 200ull * 1000ull * 1000ull;   // a wait gives up after 200 ms
 
 __device__ int g_skinny_error;     // set when a bounded wait ran out (read back by tests)
 
@@ -44,10 +48,14 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 // Bounded wait on a phase parity.  Returns false when the limit ran out or
 // another role already gave up (abort flag in shared memory).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -58,10 +66,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             : "memory");
         if (done) return true;
         if (*abort_flag) return false;
+        if ((spin & 63u) == 63u) {            // look at the clock now and then; bound the wait in TIME
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
     }
     *abort_flag = 1;
     g_skinny_error = 1;
     return false;
+}
+
+// 2-D tiled TMA load global -> this CTA's shared memory; x is the innermost
+// (K) coordinate in elements, y the row.  x * element size is a multiple of 16 bytes
+// at every call site (K steps of 64 bf16 / 64 or 128 e4m3).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
 }
 
 // K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart; the leading
@@ -96,62 +120,82 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 }
 
 struct SkinnyArgs {
-    const void* w;          // [N,K] bf16 or e4m3
     const float* w_scale;   // [N] or null
-    const void* x;          // [M,K] bf16 (modes 0,1) or e4m3 (mode 2)
-    const float* x_scale;   // [M] (mode 2) or null
+    const float* x_scale;   // [M] (W8A8) or null
     uint16_t* y;            // [M,N] bf16 ([M,N/2] behind the SwiGLU epilogue)
     uint32_t M, N, K;
     uint32_t splits, kb_per_split;   // splits = cluster size along x
     uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
+    uint32_t op_stages, raw_stages;  // ring depths (<= 8), chosen by the launcher from the grid size
 };
 
 // swizzled byte offset of 16-byte chunk `cc` (0..7) of tile row `row`
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t cc) { return row * kRowBytes + ((cc ^ (row & 7u)) << 4); }
 
+// Stage geometry per mode; the ring depth is a launch parameter (as many stages as fit in
+// half an SM's shared memory).
+template <int MODE, int NPAD> struct Ring {
+    static constexpr int BK = MODE == SKINNY_W8A8 ? 128 : 64;                    // K elements per stage
+    static constexpr uint32_t A_OP = kTileN * kRowBytes;                         // operand A stage (16 KB)
+    static constexpr uint32_t B_OP = NPAD * kRowBytes;                           // operand B stage
+    static constexpr uint32_t A_RAW = MODE == SKINNY_W_E4M3 ? kTileN * 64 : 0;   // raw e4m3 stage (8 KB)
+    static constexpr uint32_t bytes(uint32_t ops, uint32_t raws) { return ops * (A_OP + B_OP) + raws * A_RAW; }
+};
+
 }  // namespace
 
 // MODE: SKINNY_W_BF16 / SKINNY_W_E4M3 / SKINNY_W8A8.  NPAD: MMA N (16, 32 or 64).
 template <int MODE, int NPAD>
-__global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyArgs a) {
-    constexpr int WBYTES = MODE == SKINNY_W_BF16 ? 2 : 1;          // bytes per weight element in global memory
-    constexpr int XBYTES = MODE == SKINNY_W8A8 ? 1 : 2;
-    constexpr int BK = MODE == SKINNY_W8A8 ? 128 : 64;             // K elements per stage
-    constexpr int A_CPR = BK * WBYTES / 16;                        // 16-byte global chunks per weight row per stage
-    constexpr int A_PER = kTileN * A_CPR / kProducerThreads;       // ... per producer thread
-    constexpr int B_CHUNKS = NPAD * 8;                             // 16-byte chunks of the activation tile
-    constexpr int B_PER = (B_CHUNKS + kProducerThreads - 1) / kProducerThreads;
-    constexpr uint32_t A_STAGE = kTileN * kRowBytes, B_STAGE = NPAD * kRowBytes;
+__global__ void __launch_bounds__(kThreads, 2)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const SkinnyArgs a) {
+    using G = Ring<MODE, NPAD>;
+    constexpr int BK = G::BK;
+    const uint32_t OPS = a.op_stages, RAWS = a.raw_stages;
     constexpr uint32_t TMEM_COLS = NPAD < 32 ? 32 : NPAD;
     constexpr uint32_t IDESC = (1u << 4) | (MODE == SKINNY_W8A8 ? 0u : ((1u << 7) | (1u << 10))) |
                                ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+    constexpr bool E4 = MODE == SKINNY_W_E4M3;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * kStages + 1];
+    // barriers: op_full[6] (TMA bytes landed: A+B, or B only for e4m3), op_empty[6] (MMA done with the
+    // stage), conv_done[6] (e4m3: operand A written), raw_full[6], raw_empty[6], accum
+    __shared__ __align__(8) uint64_t bars[41];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sA = base, sB = base + kStages * A_STAGE;
+    const uint32_t sA = base, sB = base + OPS * G::A_OP, sRaw = sB + OPS * G::B_OP;
     const uint32_t bar0 = smem_u32(bars);
-    auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
-    const uint32_t accum_bar = bar0 + 8u * (2 * kStages);
+    auto op_full = [&](uint32_t s) { return bar0 + 8u * s; };
+    auto op_empty = [&](uint32_t s) { return bar0 + 8u * (8 + s); };
+    auto conv_done = [&](uint32_t s) { return bar0 + 8u * (16 + s); };
+    auto raw_full = [&](uint32_t s) { return bar0 + 8u * (24 + s); };
+    auto raw_empty = [&](uint32_t s) { return bar0 + 8u * (32 + s); };
+    const uint32_t accum_bar = bar0 + 8u * 40;
 
     const uint32_t tile = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
     const uint32_t nkb = (a.K + BK - 1) / BK;
-    const uint32_t kb0 = split * a.kb_per_split;
+    const uint32_t kb0 = min(nkb, split * a.kb_per_split);
     const uint32_t kb1 = min(nkb, kb0 + a.kb_per_split);
-    const uint32_t n0 = tile * kTileN;
+    const uint32_t nloc = kb1 - kb0;
+    const int32_t n0 = (int32_t)(tile * kTileN);
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), kProducerThreads); mbar_init(empty_bar(s), 1); }
+        for (uint32_t s = 0; s < 8; ++s) {
+            mbar_init(op_full(s), 1);
+            mbar_init(op_empty(s), 1);
+            mbar_init(conv_done(s), kConvThreads);
+            mbar_init(raw_full(s), 1);
+            mbar_init(raw_empty(s), kConvThreads);
+        }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     }
-    if (warp == 0) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -161,125 +205,119 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
     const uint32_t tmem_base = tmem_slot;
     volatile int* abortp = &abort_flag;
 
-    if (warp < kProducerThreads / 32) {
-        // ------------------------------------------------------------------ producers
-        const uint8_t* wg = reinterpret_cast<const uint8_t*>(a.w);
-        const uint8_t* xg = reinterpret_cast<const uint8_t*>(a.x);
-        uint4 ra[2][A_PER];
-        uint4 rb[2][B_PER];
-        auto load_a = [&](int slot, uint32_t kb) {
-#pragma unroll
-            for (int i = 0; i < A_PER; ++i) {
-                const uint32_t c = tid + kProducerThreads * i, row = c / A_CPR, cc = c % A_CPR;
-                const uint32_t n = n0 + row, k = kb * BK + cc * (16 / WBYTES);
-                ra[slot][i] = (kb < kb1 && n < a.N && k < a.K)
-                                  ? ld_stream16(wg + ((size_t)n * a.K + k) * WBYTES)
-                                  : make_uint4(0u, 0u, 0u, 0u);
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            // W ring: operand ring (bf16 / W8A8) or raw ring (e4m3).  X always lands in the operand ring.
+            const uint32_t WS = E4 ? RAWS : OPS;
+            constexpr uint32_t W_BYTES = E4 ? G::A_RAW : G::A_OP;
+            const uint32_t pre = nloc < WS ? nloc : WS;
+            // weights do not depend on the kernel that produces x: first ring-full now
+            for (uint32_t it = 0; it < pre; ++it) {
+                const uint32_t bar = E4 ? raw_full(it) : op_full(it);
+                mbar_expect_tx(bar, W_BYTES + (E4 ? 0u : G::B_OP));
+                tma_load_2d((E4 ? sRaw : sA) + it * W_BYTES, &map_w, bar, (int32_t)((kb0 + it) * BK), n0);
             }
-        };
-        auto load_b = [&](int slot, uint32_t kb) {
-#pragma unroll
-            for (int i = 0; i < B_PER; ++i) {
-                const uint32_t c = tid + kProducerThreads * i, row = c >> 3, cc = c & 7u;
-                const uint32_t k = kb * BK + cc * (16 / XBYTES);
-                rb[slot][i] = (kb < kb1 && c < B_CHUNKS && row < a.M && k < a.K)
-                                  ? *reinterpret_cast<const uint4*>(xg + ((size_t)row * a.K + k) * XBYTES)
-                                  : make_uint4(0u, 0u, 0u, 0u);
-            }
-        };
-        auto store_stage = [&](int slot, int s) {
-#pragma unroll
-            for (int i = 0; i < A_PER; ++i) {
-                const uint32_t c = tid + kProducerThreads * i, row = c / A_CPR, cc = c % A_CPR;
-                const uint4 v = ra[slot][i];
-                if constexpr (MODE == SKINNY_W_E4M3) {
-                    // 16 codes -> 16 bf16 holding value * 2^-120 (two 16-byte chunks)
-                    uint4 lo, hi;
-                    lo.x = e4m3x2_to_bf16x2_scaled<0x1404u>(v.x); lo.y = e4m3x2_to_bf16x2_scaled<0x3424u>(v.x);
-                    lo.z = e4m3x2_to_bf16x2_scaled<0x1404u>(v.y); lo.w = e4m3x2_to_bf16x2_scaled<0x3424u>(v.y);
-                    hi.x = e4m3x2_to_bf16x2_scaled<0x1404u>(v.z); hi.y = e4m3x2_to_bf16x2_scaled<0x3424u>(v.z);
-                    hi.z = e4m3x2_to_bf16x2_scaled<0x1404u>(v.w); hi.w = e4m3x2_to_bf16x2_scaled<0x3424u>(v.w);
-                    const uint32_t o0 = sA + s * A_STAGE + swz(row, 2 * cc), o1 = sA + s * A_STAGE + swz(row, 2 * cc + 1);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(o0), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(o1), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
-                } else {
-                    const uint32_t o = sA + s * A_STAGE + swz(row, cc);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(o), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            pdl_trigger();
+            pdl_wait();
+            bool ok = true;
+            uint32_t itx = 0;   // next X stage to issue
+            auto issue_x = [&](uint32_t it) {
+                const uint32_t s = it % OPS;
+                if (it >= OPS) ok = ok && mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp);
+                if (!ok) return;
+                if (E4) mbar_expect_tx(op_full(s), G::B_OP);
+                tma_load_2d(sB + s * G::B_OP, &map_x, op_full(s), (int32_t)((kb0 + it) * BK), 0);
+            };
+            if constexpr (!E4) {
+                for (; itx < pre && ok; ++itx) issue_x(itx);              // X of the prefetched stages
+                for (uint32_t it = pre; it < nloc && ok; ++it) {          // steady state: W and X together
+                    const uint32_t s = it % OPS;
+                    ok = mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp);
+                    if (!ok) break;
+                    mbar_expect_tx(op_full(s), G::A_OP + G::B_OP);
+                    tma_load_2d(sA + s * G::A_OP, &map_w, op_full(s), (int32_t)((kb0 + it) * BK), n0);
+                    tma_load_2d(sB + s * G::B_OP, &map_x, op_full(s), (int32_t)((kb0 + it) * BK), 0);
                 }
-            }
-#pragma unroll
-            for (int i = 0; i < B_PER; ++i) {
-                const uint32_t c = tid + kProducerThreads * i, row = c >> 3, cc = c & 7u;
-                if (c < B_CHUNKS) {
-                    uint4 v = rb[slot][i];
-                    if constexpr (MODE == SKINNY_W_E4M3) {
-                        // x * 2^64 (exact): keeps the products of the 2^-120-scaled weights
-                        // well inside the fp32 normal range; undone in the epilogue.
-                        const uint32_t two64 = 0x5F805F80u;
-                        asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v.x) : "r"(two64));
-                        asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v.y) : "r"(two64));
-                        asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v.z) : "r"(two64));
-                        asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v.w) : "r"(two64));
+            } else {
+                uint32_t itw = pre;
+                while ((itw < nloc || itx < nloc) && ok) {
+                    if (itx < nloc && itx < itw) { issue_x(itx); ++itx; }   // X never runs ahead of its raw W
+                    if (itw < nloc && ok) {
+                        const uint32_t s = itw % RAWS;
+                        ok = mbar_wait(raw_empty(s), ((itw / RAWS) - 1u) & 1u, abortp);
+                        if (!ok) break;
+                        mbar_expect_tx(raw_full(s), G::A_RAW);
+                        tma_load_2d(sRaw + s * G::A_RAW, &map_w, raw_full(s), (int32_t)((kb0 + itw) * BK), n0);
+                        ++itw;
                     }
-                    const uint32_t o = sB + s * B_STAGE + swz(row, cc);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(o), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                 }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            bool ok = true;
+            for (uint32_t it = 0; it < nloc && ok; ++it) {
+                const uint32_t s = it % OPS;
+                const uint32_t par = (it / OPS) & 1u;
+                ok = mbar_wait(op_full(s), par, abortp);
+                if (ok && E4) ok = mbar_wait(conv_done(s), par, abortp);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = make_desc(sA + s * G::A_OP), db = make_desc(sB + s * G::B_OP);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // 4 x (K = 32 bytes) per 128-byte row
+                    mma_issue<MODE == SKINNY_W8A8>(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), IDESC,
+                                                   (it > 0 || k > 0) ? 1u : 0u);
+                mma_commit(op_empty(s));      // frees the stage once the MMAs have read it
+            }
+            if (ok && nloc > 0) mma_commit(accum_bar);
+        }
+    } else if constexpr (E4) {
+        // ---------------------------------------------------------------- e4m3 -> bf16 widening
+        // thread -> (row, 16-byte raw chunk): a quarter warp covers 8 rows of one chunk column, which
+        // makes the swizzled 16-byte stores of the operand tile bank-conflict free.
+        const uint32_t ct = tid - 64u;
+        bool ok = true;
+        for (uint32_t it = 0; it < nloc && ok; ++it) {
+            const uint32_t sr = it % RAWS, so = it % OPS;
+            ok = mbar_wait(raw_full(sr), (it / RAWS) & 1u, abortp);
+            if (ok && it >= OPS) ok = mbar_wait(op_empty(so), ((it / OPS) - 1u) & 1u, abortp);
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t c = ct + kConvThreads * i;            // 0..511
+                const uint32_t row = (c & 7u) | ((c >> 5) << 3), cc = (c >> 3) & 3u;
+                uint4 v;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                             : "r"(sRaw + sr * G::A_RAW + row * 64u + cc * 16u));
+                const uint32_t two120 = 0x7B807B80u;                  // 2^120 as bf16x2
+                uint32_t o[8];
+                o[0] = e4m3x2_to_bf16x2_scaled<0x1404u>(v.x); o[1] = e4m3x2_to_bf16x2_scaled<0x3424u>(v.x);
+                o[2] = e4m3x2_to_bf16x2_scaled<0x1404u>(v.y); o[3] = e4m3x2_to_bf16x2_scaled<0x3424u>(v.y);
+                o[4] = e4m3x2_to_bf16x2_scaled<0x1404u>(v.z); o[5] = e4m3x2_to_bf16x2_scaled<0x3424u>(v.z);
+                o[6] = e4m3x2_to_bf16x2_scaled<0x1404u>(v.w); o[7] = e4m3x2_to_bf16x2_scaled<0x3424u>(v.w);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(o[j]) : "r"(two120));   // exact
+                const uint32_t d0 = sA + so * G::A_OP + swz(row, 2 * cc), d1 = sA + so * G::A_OP + swz(row, 2 * cc + 1);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(d0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(d1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(full_bar(s));
-        };
-
-        // weights do not depend on the producer kernel of x: two stages go out now
-        load_a(0, kb0);
-        load_a(1, kb0 + 1);
-        pdl_trigger();
-        pdl_wait();
-        load_b(0, kb0);
-        load_b(1, kb0 + 1);
-        bool ok = true;
-        uint32_t it = 0;
-        for (uint32_t kb = kb0; kb < kb1 && ok; kb += 2) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                if (kb + j < kb1 && ok) {
-                    const int s = it % kStages;
-                    const uint32_t round = it / kStages;
-                    if (round > 0) ok = mbar_wait(empty_bar(s), (round - 1) & 1u, abortp);
-                    if (ok) {
-                        store_stage(j, s);
-                        load_a(j, kb + j + 2);
-                        load_b(j, kb + j + 2);
-                    }
-                    ++it;
-                }
-            }
+            mbar_arrive(conv_done(so));
+            mbar_arrive(raw_empty(sr));
         }
-    } else if (lane == 0) {
-        // ------------------------------------------------------------------ MMA issuer
-        uint32_t it = 0;
-        bool ok = true;
-        for (uint32_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-            const int s = it % kStages;
-            ok = mbar_wait(full_bar(s), (it / kStages) & 1u, abortp);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = make_desc(sA + s * A_STAGE), db = make_desc(sB + s * B_STAGE);
-#pragma unroll
-            for (int k = 0; k < 4; ++k)   // 4 x (K = 32 bytes) per 128-byte row
-                mma_issue<MODE == SKINNY_W8A8>(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), IDESC,
-                                               (kb > kb0 || k > 0) ? 1u : 0u);
-            mma_commit(empty_bar(s));     // frees the stage once the MMAs have read it
-        }
-        if (ok) mma_commit(accum_bar);
     }
 
     // ---------------------------------------------------------------------- epilogue
     // (1) accumulator -> this CTA's shared memory, red[m][n_local] fp32 (the ring is free:
     //     every MMA that read it has completed once accum_bar fires)
     float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
-    if (warp < 4) {
-        const bool have = kb1 > kb0;
-        const bool ok = have && mbar_wait(accum_bar, 0u, abortp);
+    if (warp >= 2 && warp < 6) {
+        const uint32_t q = warp & 3u;       // the TMEM lane quarter this warp may read
+        const bool ok = nloc > 0 && mbar_wait(accum_bar, 0u, abortp);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int c0 = 0; c0 < NPAD; c0 += 16) {
@@ -287,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
 #pragma unroll
             for (int j = 0; j < 16; ++j) r[j] = 0u;
             if (ok) {
-                const uint32_t taddr = tmem_base + ((warp * 32u) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
@@ -297,59 +335,59 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) red[(c0 + j) * kTileN + warp * 32u + lane] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) red[(c0 + j) * kTileN + q * 32u + lane] = __uint_as_float(r[j]);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     // (2) every CTA of the cluster has published its partial tile
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-    // (3) this CTA finishes a contiguous slice of the tile: fixed rank order over the cluster
+    // (3) this CTA finishes a contiguous slice of the tile: fixed rank order over the cluster.
+    //     Four consecutive features per thread and step; the (up to 8) remote reads of a
+    //     step are issued together, then summed in rank order.
     {
         const uint32_t S = a.splits, rank = split;
         const uint32_t red_s = smem_u32(red);
         const bool failed = *abortp != 0;
-        if (!a.swiglu) {
-            const uint32_t total = a.M * kTileN;
-            const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
-            for (uint32_t e = lo + tid; e < hi; e += kThreads) {
-                const uint32_t m = e / kTileN, nl = e % kTileN, n = n0 + nl;
-                float acc = 0.f;
-                for (uint32_t r = 0; r < S; ++r) {
+        const uint32_t total = a.M * (kTileN / 4);                 // float4 units
+        const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
+        for (uint32_t e = lo + tid; e < hi; e += kThreads) {
+            const uint32_t m = e / (kTileN / 4), nl = (e % (kTileN / 4)) * 4u, n = (uint32_t)n0 + nl;
+            float4 v[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) {
+                v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < S) {
                     uint32_t ra;
-                    float v;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 4u * e), "r"(r));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-                    acc += v;
-                }
-                if (n < a.N && !failed) {
-                    if constexpr (MODE == SKINNY_W_E4M3) acc *= 7.205759403792794e16f;   // 2^56 = 2^120 / 2^64
-                    if (a.w_scale != nullptr) acc *= a.w_scale[n];
-                    if (MODE == SKINNY_W8A8) acc *= a.x_scale[m];
-                    a.y[(size_t)m * a.N + n] = f32_to_bf16_bits(acc);
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 16u * e), "r"(r));
+                    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w) : "r"(ra) : "memory");
                 }
             }
-        } else {
-            const uint32_t half = kTileN / 2, total = a.M * half;
-            const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
-            for (uint32_t e = lo + tid; e < hi; e += kThreads) {
-                const uint32_t m = e / half, p = e % half, n = n0 + 2u * p;
-                float gt = 0.f, up = 0.f;
-                for (uint32_t r = 0; r < S; ++r) {
-                    uint32_t ra;
-                    float2 v;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 4u * (m * kTileN + 2u * p)), "r"(r));
-                    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(ra) : "memory");
-                    gt += v.x;
-                    up += v.y;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r)
+                if (r < S) { acc[0] += v[r].x; acc[1] += v[r].y; acc[2] += v[r].z; acc[3] += v[r].w; }
+            if (failed) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (n + j < a.N) {
+                    if (a.w_scale != nullptr) acc[j] *= a.w_scale[n + j];
+                    if (MODE == SKINNY_W8A8) acc[j] *= a.x_scale[m];
                 }
-                if (n + 1 < a.N && !failed) {
-                    if constexpr (MODE == SKINNY_W_E4M3) { gt *= 7.205759403792794e16f; up *= 7.205759403792794e16f; }
-                    if (a.w_scale != nullptr) { gt *= a.w_scale[n]; up *= a.w_scale[n + 1]; }
-                    if (MODE == SKINNY_W8A8) { gt *= a.x_scale[m]; up *= a.x_scale[m]; }
-                    const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(gt) << 16);
-                    const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
-                    a.y[(size_t)m * (a.N / 2u) + (n >> 1)] = f32_to_bf16_bits(swiglu_f32(gb, ub));
+            }
+            if (!a.swiglu) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (n + j < a.N) a.y[(size_t)m * a.N + n + j] = f32_to_bf16_bits(acc[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j += 2) {
+                    if (n + j + 1 < a.N) {
+                        const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(acc[j]) << 16);
+                        const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(acc[j + 1]) << 16);
+                        a.y[(size_t)m * (a.N / 2u) + ((n + j) >> 1)] = f32_to_bf16_bits(swiglu_f32(gb, ub));
+                    }
                 }
             }
         }
@@ -358,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyAr
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
@@ -369,8 +407,8 @@ namespace {
 
 struct Plan { uint32_t tiles, splits, kb_per_split; };
 
-// Cluster size along K: the largest of 8/4/2/1 that keeps the grid within two CTAs
-// per SM and leaves every CTA at least two K blocks.
+// Cluster size along K: the largest of 8/4/2/1 that keeps the grid within two CTAs per SM
+// and leaves every CTA at least two K blocks.
 Plan make_plan(uint32_t N, uint32_t K, uint32_t bk) {
     Plan p;
     p.tiles = (N + kTileN - 1) / kTileN;
@@ -383,20 +421,76 @@ Plan make_plan(uint32_t N, uint32_t K, uint32_t bk) {
     return p;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Row-major [rows, K] matrix of 1- or 2-byte elements, box = [box_rows x box_k]; out-of-range
+// rows / columns read as zero (ragged N, M < Mpad, K tail).
+mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
+                     uint32_t box_k, uint32_t box_rows, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) {
+        set_error("skinny_gemm: cuTensorMapEncodeTiled is not available from this driver");
+        return MC_E_CUDA;
+    }
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * elem_bytes};
+    const cuuint32_t box[2] = {box_k, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                          const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("skinny_gemm: cuTensorMapEncodeTiled failed (%d) for rows=%u K=%u", (int)r, rows, K);
+        return MC_E_CUDA;
+    }
+    return MC_OK;
+}
+
 template <int MODE, int NPAD>
-mc_status_t launch_one(const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
-    constexpr size_t smem = (size_t)kStages * (kTileN + NPAD) * kRowBytes + 1024;
-    static_assert((size_t)NPAD * kTileN * 4 <= (size_t)kStages * (kTileN + NPAD) * kRowBytes, "reduce tile must fit in the ring");
+mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
+    using G = Ring<MODE, NPAD>;
+    static_assert((size_t)NPAD * kTileN * 4 <= (size_t)G::bytes(3, 0), "reduce tile must fit in the ring");
     auto kern = skinny_gemm_kernel<MODE, NPAD>;
+    constexpr size_t smem_max = 112u * 1024u;
     static bool attr_done = false;
     if (!attr_done) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
         if (e != cudaSuccess) {
-            set_error("skinny_gemm: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+            set_error("skinny_gemm: cannot raise shared memory to %zu: %s", smem_max, cudaGetErrorString(e));
             return MC_E_CUDA;
         }
         attr_done = true;
     }
+    const size_t smem = (size_t)G::bytes(a.op_stages, MODE == SKINNY_W_E4M3 ? a.raw_stages : 0) + 1024;
+    CUtensorMap map_w, map_x;
+    mc_status_t s;
+    if (MODE == SKINNY_W_BF16) {
+        s = make_map(&map_w, w, a.N, a.K, 2, 64, kTileN, true);
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 2, 64, NPAD, true);
+    } else if (MODE == SKINNY_W_E4M3) {
+        s = make_map(&map_w, w, a.N, a.K, 1, 64, kTileN, false);      // raw codes, widened by warps 2-9
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 2, 64, NPAD, true);
+    } else {
+        s = make_map(&map_w, w, a.N, a.K, 1, 128, kTileN, true);
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 1, 128, NPAD, true);
+    }
+    if (s != MC_OK) return s;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -411,20 +505,21 @@ mc_status_t launch_one(const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, 
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 2 : 1;
-    (void)cudaLaunchKernelEx(&cfg, kern, a);
+    (void)cudaLaunchKernelEx(&cfg, kern, map_w, map_x, a);
     MCL_CHECK_LAUNCH("skinny_gemm");
     return MC_OK;
 }
 
 template <int MODE>
-mc_status_t launch_mode(const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
-    if (a.M <= 16) return launch_one<MODE, 16>(a, grid, stream, pdl);
-    if (a.M <= 32) return launch_one<MODE, 32>(a, grid, stream, pdl);
-    return launch_one<MODE, 64>(a, grid, stream, pdl);
+mc_status_t launch_mode(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
+    if (a.M <= 16) return launch_one<MODE, 16>(w, x, a, grid, stream, pdl);
+    if (a.M <= 32) return launch_one<MODE, 32>(w, x, a, grid, stream, pdl);
+    return launch_one<MODE, 64>(w, x, a, grid, stream, pdl);
 }
 
 }  // namespace
 
+// TMA needs 16-byte aligned row pitches: K % 8 (bf16 rows) and K % 16 (e4m3 rows).
 bool skinny_shape_ok(uint32_t N, uint32_t K, int wb) {
     return N > 0 && K > 0 && (K % (wb == 2 ? 8u : 16u)) == 0;
 }
@@ -440,12 +535,27 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
     }
     const Plan p = make_plan(N, K, mode == SKINNY_W8A8 ? 128u : 64u);
     SkinnyArgs a{};
-    a.w = w; a.w_scale = w_scale; a.x = x; a.x_scale = x_scale; a.y = y;
+    a.w_scale = w_scale; a.x_scale = x_scale; a.y = y;
     a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.kb_per_split = p.kb_per_split; a.swiglu = swiglu ? 1u : 0u;
     const uint32_t grid = p.tiles * p.splits;
-    if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(a, grid, stream, pdl);
-    if (mode == SKINNY_W_E4M3) return launch_mode<SKINNY_W_E4M3>(a, grid, stream, pdl);
-    return launch_mode<SKINNY_W8A8>(a, grid, stream, pdl);
+    // Ring depth: as many stages as fit in ~108 KB, i.e. half an SM's shared memory.  Measured:
+    // a deeper ring that fills the SM is slower in a chain of launches, because the next
+    // kernel's CTA can then no longer become resident (and prefetch its weights) while this
+    // one drains.
+    const uint32_t npad = M <= 16 ? 16u : (M <= 32 ? 32u : 64u);
+    const uint32_t op_stage = (uint32_t)(kTileN + npad) * kRowBytes, budget = 108u * 1024u;
+    if (mode == SKINNY_W_E4M3) {
+        a.op_stages = 3u;
+        a.raw_stages = (budget - 3u * op_stage) / (kTileN * 64u);
+        if (a.raw_stages > 8u) a.raw_stages = 8u;
+    } else {
+        a.op_stages = budget / op_stage;
+        if (a.op_stages > 8u) a.op_stages = 8u;
+        a.raw_stages = 1u;
+    }
+    if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(w, x, a, grid, stream, pdl);
+    if (mode == SKINNY_W_E4M3) return launch_mode<SKINNY_W_E4M3>(w, x, a, grid, stream, pdl);
+    return launch_mode<SKINNY_W8A8>(w, x, a, grid, stream, pdl);
 }
 
 // 1 when a bounded wait of the tensor-core kernel ran out since the last call (and clears it).

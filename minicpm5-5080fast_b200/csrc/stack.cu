@@ -1,0 +1,290 @@
+// stack.cu -- the decode linear stack as one host-side object: weight-arena layout,
+// linear dispatch per step, CUDA-graph replay, host-buffer step.
+//
+// This is the slice of the reference's executors that belongs to the linear path:
+// the per-layer dispatch of run_real_forward (native/runtime/forward.cpp:98-160,
+// 206-237, 306-373, 443-462) and of mc_batch_step (native/runtime/batch_group.cpp:745-807),
+// the compact 256-byte-aligned placement of the weight sections
+// (native/runtime/weight_loader.cpp:355-365, 563-630) and the capture / replay of a
+// step (native/runtime/decode_executor.cpp:163-209).  Attention, RoPE/KV and sampling
+// beyond greedy are not part of it: the attention block is stood in for by taking the
+// first `hidden` features of the fused qkv output.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace mcl {
+
+enum : uint32_t {
+    SEC_QKV = 0, SEC_O = 1, SEC_GATE_UP = 2, SEC_DOWN = 3, SEC_NORM1 = 4, SEC_NORM2 = 5,
+    SEC_QKV_SCALE = 6, SEC_O_SCALE = 7, SEC_GATE_UP_SCALE = 8, SEC_DOWN_SCALE = 9,
+    SEC_LM_HEAD = 10, SEC_FINAL_NORM = 11, SEC_LM_HEAD_SCALE = 12, SEC_COUNT = 13
+};
+
+static inline size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+struct Layout {
+    size_t per_layer[10];      // byte size of SEC_QKV .. SEC_DOWN_SCALE (0 when absent)
+    size_t layer_off[10];      // offset inside one layer block
+    size_t layer_bytes;        // pitch of a layer block
+    size_t top_off[3], top_bytes[3];   // lm_head, final_norm, lm_head_scale
+    size_t total;
+};
+
+static bool valid_desc(const mc_sm100_stack_desc_t* d) {
+    if (d == nullptr || d->struct_size != sizeof(mc_sm100_stack_desc_t)) return false;
+    if (d->layers == 0 || d->hidden == 0 || d->qkv_rows < d->hidden || d->inter == 0 || d->vocab == 0) return false;
+    if (d->precision != 0u && d->precision != 2u) return false;
+    if (d->max_batch == 0 || d->max_batch > 64u) return false;
+    const uint32_t mult = d->precision == 2u ? 16u : 8u;
+    if (d->hidden % mult != 0 || d->inter % mult != 0) return false;
+    for (int i = 0; i < 4; ++i)
+        if (d->reserved[i] != 0) return false;
+    return true;
+}
+
+static Layout make_layout(const mc_sm100_stack_desc_t* d) {
+    Layout L{};
+    const size_t wb = d->precision == 2u ? 1u : 2u;
+    const size_t H = d->hidden, Q = d->qkv_rows, I = d->inter, V = d->vocab;
+    const bool fp8 = d->precision == 2u;
+    const size_t sizes[10] = {Q * H * wb, H * H * wb, 2 * I * H * wb, H * I * wb, H * 2, H * 2,
+                              fp8 ? Q * 4 : 0, fp8 ? H * 4 : 0, fp8 ? 2 * I * 4 : 0, fp8 ? H * 4 : 0};
+    size_t off = 0;
+    for (int i = 0; i < 10; ++i) {
+        L.per_layer[i] = sizes[i];
+        L.layer_off[i] = off;
+        off += align256(sizes[i]);
+    }
+    L.layer_bytes = off;
+    size_t top = L.layer_bytes * d->layers;
+    const size_t tops[3] = {V * H * wb, H * 2, fp8 ? V * 4 : 0};
+    for (int i = 0; i < 3; ++i) {
+        L.top_off[i] = top;
+        L.top_bytes[i] = tops[i];
+        top += align256(tops[i]);
+    }
+    L.total = top;
+    return L;
+}
+
+// activation scratch (bf16 unless noted), all 256-byte aligned
+struct Scratch {
+    size_t x, res_a, res_b, h, qkv, ctx, o, mid, down, logits, stage, tokens, vals, total;
+};
+
+static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
+    Scratch s{};
+    const size_t M = d->max_batch, H = d->hidden;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += align256(bytes); return at; };
+    s.x = take(M * H * 2); s.res_a = take(M * H * 2); s.res_b = take(M * H * 2); s.h = take(M * H * 2);
+    s.qkv = take(M * d->qkv_rows * 2); s.ctx = take(M * H * 2); s.o = take(M * H * 2);
+    s.mid = take(M * (size_t)d->inter * 2); s.down = take(M * H * 2); s.logits = take(M * (size_t)d->vocab * 2);
+    s.stage = take(mc_sm100_argmax_stage_bytes(d->max_batch)); s.tokens = take(M * 4); s.vals = take(M * 4);
+    s.total = off;
+    return s;
+}
+
+}  // namespace mcl
+
+using namespace mcl;
+
+struct mc_sm100_stack {
+    mc_sm100_stack_desc_t desc;
+    Layout lay;
+    Scratch scr;
+    uint8_t* w;
+    uint8_t* s;
+    cudaGraphExec_t graph[65];     // per batch size, captured lazily
+    cudaStream_t graph_stream[65];
+};
+
+static const void* sec(const mc_sm100_stack* st, uint32_t layer, uint32_t which) {
+    if (which < 10) return st->lay.per_layer[which] ? st->w + st->lay.layer_bytes * layer + st->lay.layer_off[which] : nullptr;
+    return st->lay.top_bytes[which - 10] ? st->w + st->lay.top_off[which - 10] : nullptr;
+}
+
+// One step for M rows; every launch goes to `stream`, nothing synchronises.
+static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, cudaStream_t stream) {
+    const mc_sm100_stack_desc_t& d = st->desc;
+    const uint32_t H = d.hidden, Q = d.qkv_rows, I = d.inter, V = d.vocab;
+    const bool fp8 = d.precision == 2u;
+    auto buf = [&](size_t off) { return reinterpret_cast<uint16_t*>(st->s + off); };
+    uint16_t *ra = buf(st->scr.res_a), *rb = buf(st->scr.res_b), *h = buf(st->scr.h), *qkv = buf(st->scr.qkv),
+             *ctx = buf(st->scr.ctx), *o = buf(st->scr.o), *mid = buf(st->scr.mid), *dn = buf(st->scr.down),
+             *logits = buf(st->scr.logits);
+    void* stage = st->s + st->scr.stage;
+    float* vals = reinterpret_cast<float*>(st->s + st->scr.vals);
+    void* sp = (void*)stream;
+    mc_status_t rc = MC_OK;
+#define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
+    if (M == 1) {
+        // fused chain: residual add + RMSNorm live in the GEMV prologues, SwiGLU in the gate_up epilogue
+        const uint16_t* res_in = d_x;
+        const uint16_t* addend = nullptr;
+        for (uint32_t l = 0; l < d.layers; ++l) {
+            const uint16_t *n1 = (const uint16_t*)sec(st, l, SEC_NORM1), *n2 = (const uint16_t*)sec(st, l, SEC_NORM2);
+            if (fp8) STEP(mc_sm100_gemv_fp8_prologue((const uint8_t*)sec(st, l, SEC_QKV), (const float*)sec(st, l, SEC_QKV_SCALE), res_in, addend, n1, rb, qkv, Q, H, d.eps, sp, 1));
+            else STEP(mc_sm100_gemv_rows_prologue((const uint16_t*)sec(st, l, SEC_QKV), res_in, addend, n1, rb, qkv, Q, H, d.eps, sp, 1));
+            if (fp8) STEP(mc_sm100_gemv_fp8((const uint8_t*)sec(st, l, SEC_O), (const float*)sec(st, l, SEC_O_SCALE), qkv, o, H, H, sp, 1));
+            else STEP(mc_sm100_decode_gemv((const uint16_t*)sec(st, l, SEC_O), qkv, o, H, H, MC_GEMV_TACTIC_ROWS, 0, nullptr, sp, 1));
+            STEP(mc_sm100_gate_up_swiglu_prologue(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), rb, o, n2, ra, mid, 2 * I, H, d.eps, sp, 1));
+            if (fp8) STEP(mc_sm100_gemv_fp8((const uint8_t*)sec(st, l, SEC_DOWN), (const float*)sec(st, l, SEC_DOWN_SCALE), mid, dn, H, I, sp, 1));
+            else STEP(mc_sm100_decode_gemv((const uint16_t*)sec(st, l, SEC_DOWN), mid, dn, H, I, MC_GEMV_TACTIC_ROWS, 0, nullptr, sp, 1));
+            res_in = ra;
+            addend = dn;
+        }
+        STEP(mc_sm100_lm_head_argmax_prologue(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), res_in, addend,
+                                              (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), rb, logits, V, H, d.eps, 0, stage,
+                                              d_tokens, vals, sp, 1));
+        return MC_OK;
+    }
+    // batched chain: separate residual+RMSNorm kernels between the tensor-core GEMMs
+    cudaError_t e = cudaMemcpyAsync(ra, d_x, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    auto linear = [&](uint32_t l, uint32_t wsec, uint32_t ssec, const uint16_t* x, uint16_t* y, uint32_t N, uint32_t K) {
+        return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, l, wsec), (const float*)sec(st, l, ssec), x, y, M, N, K, sp, 1)
+                   : mc_sm100_gemm_bf16(sp, nullptr, 0, M, N, K, sec(st, l, wsec), x, y);
+    };
+    const uint16_t* addend = nullptr;
+    for (uint32_t l = 0; l < d.layers; ++l) {
+        STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps, sp, 1));
+        STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, qkv, Q, H));
+        e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, qkv, (size_t)Q * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+        STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, o, H, H));
+        STEP(mc_sm100_residual_rmsnorm_rows(ra, o, (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
+        STEP(mc_sm100_gate_up_swiglu(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), h, mid, M, 2 * I, H, sp, 1));
+        STEP(linear(l, SEC_DOWN, SEC_DOWN_SCALE, mid, dn, H, I));
+        addend = dn;
+    }
+    STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), h, M, H, d.eps, sp, 1));
+    if (M <= 8) {
+        STEP(mc_sm100_lm_head_argmax(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, V, M, V, H, 0, stage, d_tokens, vals, sp, 1));
+    } else {
+        STEP(linear(0, SEC_LM_HEAD, SEC_LM_HEAD_SCALE, h, logits, V, H));
+        STEP(mc_sm100_argmax_bf16(logits, M, V, V, 0, stage, d_tokens, vals, sp, 1));
+    }
+#undef STEP
+    return MC_OK;
+}
+
+extern "C" {
+
+mc_status_t mc_sm100_stack_sizes(const mc_sm100_stack_desc_t* desc, uint64_t* weight_bytes, uint64_t* scratch_bytes) {
+    clear_error();
+    if (!valid_desc(desc)) { set_error("mc_sm100_stack_sizes: invalid descriptor"); return MC_E_INVALID_ARGUMENT; }
+    if (weight_bytes) *weight_bytes = make_layout(desc).total;
+    if (scratch_bytes) *scratch_bytes = make_scratch(desc).total;
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_stack_section(const mc_sm100_stack_desc_t* desc, uint32_t layer, uint32_t which, uint64_t* offset,
+                                   uint64_t* bytes) {
+    clear_error();
+    if (!valid_desc(desc) || which >= SEC_COUNT || (which < 10 && layer >= desc->layers) || offset == nullptr || bytes == nullptr) {
+        set_error("mc_sm100_stack_section: invalid args (layer=%u which=%u)", layer, which);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    const Layout L = make_layout(desc);
+    if (which < 10) { *offset = L.layer_bytes * layer + L.layer_off[which]; *bytes = L.per_layer[which]; }
+    else { *offset = L.top_off[which - 10]; *bytes = L.top_bytes[which - 10]; }
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_weights, void* d_scratch,
+                                  mc_sm100_stack_t* out) {
+    clear_error();
+    if (out != nullptr) *out = nullptr;
+    if (!valid_desc(desc) || d_weights == nullptr || d_scratch == nullptr || out == nullptr ||
+        ((uintptr_t)d_weights & 255u) != 0 || ((uintptr_t)d_scratch & 255u) != 0) {
+        set_error("mc_sm100_stack_create: invalid args (descriptor, or arenas not 256-byte aligned)");
+        return MC_E_INVALID_ARGUMENT;
+    }
+    const mc_status_t dc = mc_sm100_device_check(nullptr, nullptr, nullptr, nullptr);
+    if (dc != MC_OK) return dc;
+    mc_sm100_stack* st = new (std::nothrow) mc_sm100_stack();
+    if (st == nullptr) { set_error("mc_sm100_stack_create: out of host memory"); return MC_E_OUT_OF_MEMORY; }
+    st->desc = *desc;
+    st->lay = make_layout(desc);
+    st->scr = make_scratch(desc);
+    st->w = (uint8_t*)d_weights;
+    st->s = (uint8_t*)d_scratch;
+    std::memset(st->graph, 0, sizeof(st->graph));
+    std::memset(st->graph_stream, 0, sizeof(st->graph_stream));
+    *out = st;
+    return MC_OK;
+}
+
+void mc_sm100_stack_destroy(mc_sm100_stack_t st) {
+    if (st == nullptr) return;
+    for (auto& g : st->graph)
+        if (g != nullptr) cudaGraphExecDestroy(g);
+    delete st;
+}
+
+const uint16_t* mc_sm100_stack_logits(mc_sm100_stack_t st) {
+    return st == nullptr ? nullptr : reinterpret_cast<const uint16_t*>(st->s + st->scr.logits);
+}
+
+mc_status_t mc_sm100_stack_step(mc_sm100_stack_t st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, void* stream) {
+    clear_error();
+    if (st == nullptr || d_x == nullptr || d_tokens == nullptr || M == 0 || M > st->desc.max_batch) {
+        set_error("mc_sm100_stack_step: invalid args (M=%u)", M);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    return run_step(st, d_x, M, d_tokens, (cudaStream_t)stream);
+}
+
+mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t st, const uint16_t* h_x, uint32_t M, int32_t* h_tokens, void* stream) {
+    clear_error();
+    if (st == nullptr || h_x == nullptr || h_tokens == nullptr || M == 0 || M > st->desc.max_batch) {
+        set_error("mc_sm100_stack_step_host: invalid args (M=%u)", M);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    const cudaStream_t s = (cudaStream_t)stream;
+    uint16_t* d_x = reinterpret_cast<uint16_t*>(st->s + st->scr.x);
+    int32_t* d_tok = reinterpret_cast<int32_t*>(st->s + st->scr.tokens);
+    cudaError_t e = cudaMemcpyAsync(d_x, h_x, (size_t)M * st->desc.hidden * 2, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) { set_error("stack step: H2D failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    mc_status_t rc = MC_OK;
+    if (st->desc.enable_cuda_graph && s != nullptr) {
+        if (st->graph[M] == nullptr || st->graph_stream[M] != s) {
+            // first use of this batch size on this stream: one eager step (sets kernel attributes),
+            // then capture.  A failed capture falls back to eager launches of the same kernels
+            // (the reference does the same, native/runtime/session.cpp:489-499).
+            rc = run_step(st, d_x, M, d_tok, s);
+            if (rc != MC_OK) return rc;
+            cudaGraph_t g = nullptr;
+            if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                const mc_status_t cap = run_step(st, d_x, M, d_tok, s);
+                const cudaError_t ce = cudaStreamEndCapture(s, &g);
+                if (cap == MC_OK && ce == cudaSuccess && g != nullptr) {
+                    if (st->graph[M] != nullptr) cudaGraphExecDestroy(st->graph[M]);
+                    st->graph[M] = nullptr;
+                    if (cudaGraphInstantiate(&st->graph[M], g, 0) == cudaSuccess) st->graph_stream[M] = s;
+                    else st->graph[M] = nullptr;
+                }
+                if (g != nullptr) cudaGraphDestroy(g);
+                (void)cudaGetLastError();
+            }
+        }
+        if (st->graph[M] != nullptr) {
+            e = cudaGraphLaunch(st->graph[M], s);
+            if (e != cudaSuccess) { set_error("stack step: graph launch failed: %s", cudaGetErrorString(e)); return MC_E_GRAPH; }
+        } else {
+            rc = run_step(st, d_x, M, d_tok, s);
+        }
+    } else {
+        rc = run_step(st, d_x, M, d_tok, s);
+    }
+    if (rc != MC_OK) return rc;
+    e = cudaMemcpyAsync(h_tokens, d_tok, (size_t)M * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { set_error("stack step: D2H/sync failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    return MC_OK;
+}
+
+}  // extern "C"
