@@ -306,6 +306,13 @@ class Stream:
         self.val = torch.zeros(m, dtype=torch.float32, device=dev)
         self.pair = torch.zeros((world, m, 2), dtype=torch.float32, device=dev)
         self.launches = 0
+        self.peer = None
+        if world > 1 and m == 1 and os.environ.get("MC_GATHER", "peer") == "peer":
+            try:
+                self._setup_peer(dev)
+            except Exception as e:      # no symmetric memory on this stack: NCCL all-gather, same kernels otherwise
+                self.peer = None
+                self.peer_error = f"{type(e).__name__}: {e}"[:120]
         if m != 1:
             if world != 1:
                 raise SystemExit("bench: the batched (M > 1) stream runs on one GPU")
@@ -316,7 +323,46 @@ class Stream:
             self.qkv_m, self.o_m, self.mid_m, self.dn_m = z(m, QKV), z(m, H), z(m, I), z(m, H)
             self.logits = z(m, V)
 
-    def gather(self, full, shard):
+    def _setup_peer(self, dev):
+        """Gathered buffers in symmetric (peer-mapped) memory + flag arrays for the library's own
+        all-gather kernel (mc_sm100_peer_allgather)."""
+        import torch.distributed._symmetric_memory as symm
+        torch, world, rank = self.torch, self.world, self.rank
+        slots = {"qkv": self.per["qkv"] * 2, "o": self.per["o"] * 2, "mid": self.per["mid"] * 2,
+                 "dn": self.per["down"] * 2, "pair": 16}
+        off, cur = {}, 256                                # [0,256): flag array (world x uint32)
+        for k, b in slots.items():
+            off[k] = cur
+            cur += (b * world + 255) // 256 * 256
+        t = symm.empty(cur, dtype=torch.uint8, device=dev)
+        t.zero_()
+        h = symm.rendezvous(t, self.dist.group.WORLD)
+        ptrs = [int(p) for p in h.buffer_ptrs]
+        self.sym = t
+        i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)
+        self.peer = {"slots": slots, "flags": i64(ptrs), "my_flags": t[:256].view(torch.int32),
+                     "bufs": {k: i64([p + off[k] for p in ptrs]) for k in slots},
+                     "epoch": torch.zeros(1, dtype=torch.int32, device=dev),
+                     "status": torch.zeros(1, dtype=torch.int32, device=dev)}
+        view = lambda k, n: t[off[k]:off[k] + slots[k] * world].view(torch.int16).view(world, 1, n)
+        self.qkv, self.o = view("qkv", self.per["qkv"]), view("o", self.per["o"])
+        self.mid, self.dn = view("mid", self.per["mid"]), view("dn", self.per["down"])
+        self.pair = t[off["pair"]:off["pair"] + 16 * world].view(torch.float32).view(world, 4)
+        self.pair_shard = torch.zeros(4, dtype=torch.float32, device=dev)
+        torch.cuda.synchronize()
+        self.dist.barrier()
+
+    def peer_gather(self, key, shard):
+        pr = self.peer
+        nbytes = shard.numel() * shard.element_size()
+        self.pkg.peer_allgather(shard, nbytes, pr["slots"][key], pr["bufs"][key], pr["flags"], pr["my_flags"],
+                                pr["epoch"], self.rank, self.world, status=pr["status"], pdl=True)
+        self.extra_launches += 1
+
+    def gather(self, full, shard, key=None):
+        if self.world > 1 and self.peer is not None and key is not None:
+            self.peer_gather(key, shard)
+            return full.view(-1)
         if self.world > 1:
             # NCCL has no 16-bit integer type: the same bits travel as bf16
             self.dist.all_gather_into_tensor(full.view(-1).view(self.torch.bfloat16), shard.view(-1).view(self.torch.bfloat16))
@@ -372,6 +418,7 @@ class Stream:
         if self.m != 1:
             return self.step_batched(pdl)
         p, fp8 = self.pkg, self.fp8
+        self.extra_launches = 0
         ra, rb = self.res                    # residual ping-pong: qkv reads ra -> writes rb, gate_up reads rb -> writes ra
         addend = None
         x_res = self.x_in
@@ -380,18 +427,18 @@ class Stream:
             w, s = lay["qkv"]
             (p.launch_gemv_fp8_prologue(w, s, x_res, addend, lay["n1"], rb, self.qkv_s, w.shape[0], H, 1e-6, pdl=pdl) if fp8
              else p.launch_gemv_rows_prologue(w, x_res, addend, lay["n1"], rb, self.qkv_s, w.shape[0], H, 1e-6, pdl=pdl))
-            qkv = self.gather(self.qkv, self.qkv_s)
+            qkv = self.gather(self.qkv, self.qkv_s, "qkv")
             w, s = lay["o"]
             (p.launch_gemv_fp8(w, s, qkv, self.o_s, w.shape[0], H, pdl=pdl) if fp8
              else p.launch_decode_gemv(w, qkv, self.o_s, w.shape[0], H, pdl=pdl))
-            o = self.gather(self.o, self.o_s)
+            o = self.gather(self.o, self.o_s, "o")
             w, s = lay["gu"]
             p.launch_gate_up_swiglu_prologue(w, s, rb, o, lay["n2"], ra, self.mid_s, w.shape[0], H, 1e-6, pdl=pdl)
-            mid = self.gather(self.mid, self.mid_s)
+            mid = self.gather(self.mid, self.mid_s, "mid")
             w, s = lay["down"]
             (p.launch_gemv_fp8(w, s, mid, self.dn_s, w.shape[0], I, pdl=pdl) if fp8
              else p.launch_decode_gemv(w, mid, self.dn_s, w.shape[0], I, pdl=pdl))
-            addend = self.gather(self.dn, self.dn_s)
+            addend = self.gather(self.dn, self.dn_s, "dn")
             x_res = ra
             n += 4
         a = rb
@@ -401,8 +448,14 @@ class Stream:
         n += 2
         if self.world > 1:
             # (value, index) of every shard to every rank, then the same tie rule
-            mine = self.torch.stack((self.val, self.tok.to(self.torch.float32)), dim=1)
-            self.dist.all_gather_into_tensor(self.pair.view(-1), mine.view(-1))
+            if self.peer is not None:
+                self.pair_shard[0:1].copy_(self.val)
+                self.pair_shard[1:2].copy_(self.tok.to(self.torch.float32))
+                self.peer_gather("pair", self.pair_shard)
+            else:
+                mine = self.torch.stack((self.val, self.tok.to(self.torch.float32)), dim=1)
+                self.dist.all_gather_into_tensor(self.pair.view(-1), mine.view(-1))
+        n += self.extra_launches
         self.launches = n
         return self.tok
 
@@ -542,6 +595,8 @@ def run_ours(args):
         barrier()
         ms_e2e = e0.elapsed_time(e1)
 
+    if getattr(st, "peer", None) is not None and int(st.peer["status"].item()) != 0:
+        raise SystemExit("bench: a bounded wait of the peer all-gather kernel ran out (a rank fell behind or died)")
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -563,6 +618,8 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if wb == 2 else "fp8_e4m3_weight_only(fp32 acc)",
             "data": "synthetic",
             "config": {"workload": workload_name(args), "launch": mode, "parallelism": f"N-sharded x{world}",
+                       "gather": (None if world == 1 else ("peer-store kernel over NVLink (symmetric memory)" if getattr(st, "peer", None)
+                                  else "nccl all_gather" + (" (" + getattr(st, "peer_error", "") + ")" if getattr(st, "peer_error", "") else ""))),
                        "l2": ("every call reads a different weight copy; the copies together exceed twice the L2" if single
                               else "inputs larger than L2: every step streams its own weights from HBM once"),
                        "bytes_per_step": total_bytes, "calls_per_step": st.launches if not single else st.copies,

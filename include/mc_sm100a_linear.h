@@ -336,6 +336,23 @@ MC_SM100_API const uint16_t* mc_sm100_stack_logits(mc_sm100_stack_t stack);
 MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const uint16_t* h_x, uint32_t M,
                                                   int32_t* h_tokens, void* stream);
 
+/* --------------------------------------------------------------- multi-GPU --- */
+
+/* All-gather of an N-shard over NVLink peer memory in one small kernel (no counterpart in
+ * the reference, which is single-GPU; native/include/minicpm_runtime.h:61).  Rank `rank`
+ * stores its slice (shard_bytes, a multiple of 16) at offset rank * slot_bytes of EVERY
+ * rank's gathered buffer (d_peer_bufs: device array of `world` device addresses, peer-mapped),
+ * then publishes the exchange's epoch in every rank's flag array (d_peer_flags[p] points to
+ * rank p's array of `world` uint32) and waits until its own flags (d_my_flags) show that all
+ * ranks have done the same.  d_epoch is a device counter the kernel advances itself, so the
+ * call can be captured and replayed.  The wait is bounded (timeout_ns, 0 = 1 s); if it runs
+ * out the kernel sets *d_status = 1 and returns normally.  Plain peer stores only. */
+MC_SM100_API mc_status_t mc_sm100_peer_allgather(const void* d_shard, uint32_t shard_bytes, uint32_t slot_bytes,
+                                                 const uint64_t* d_peer_bufs, const uint64_t* d_peer_flags,
+                                                 uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank,
+                                                 uint32_t world, uint64_t timeout_ns, int32_t* d_status,
+                                                 void* stream, int32_t pdl);
+
 /* ------------------------------------------------------------ packed weights --- */
 
 /* Reader of the reference's packed weight file (WPK v1: tools/minicpm_common.py:47-75,

@@ -65,6 +65,7 @@ SIGNATURES = {
     "mc_sm100_stack_logits": (_vp, [_vp]),
     "mc_sm100_stack_step": (_i32, [_vp, _vp, _u32, _vp, _vp]),
     "mc_sm100_stack_step_host": (_i32, [_vp, _vp, _u32, _vp, _vp]),
+    "mc_sm100_peer_allgather": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _i32]),
     "mc_sm100_wpk_name_hash": (C.c_uint64, [C.c_char_p]),
     "mc_sm100_wpk_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
     "mc_sm100_wpk_close": (None, [_vp]),
@@ -326,3 +327,10 @@ def wpk_find(h, name: str) -> WpkSection:
 def wpk_upload(h, name, row_lo, row_hi, interleave, dst, scale_dst=None, stream=None):
     _check(lib().mc_sm100_wpk_upload(h, name.encode(), row_lo, row_hi, int(interleave), _p(dst),
                                      dst.numel() * dst.element_size(), _p(scale_dst), _stream(stream)))
+
+
+def peer_allgather(shard, shard_bytes, slot_bytes, peer_bufs, peer_flags, my_flags, epoch, rank, world,
+                   timeout_ns=0, status=None, stream=None, pdl=False):
+    _check(lib().mc_sm100_peer_allgather(_p(shard), shard_bytes, slot_bytes, _p(peer_bufs), _p(peer_flags),
+                                         _p(my_flags), _p(epoch), rank, world, timeout_ns, _p(status),
+                                         _stream(stream), int(pdl)))

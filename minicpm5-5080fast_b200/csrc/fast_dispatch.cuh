@@ -36,38 +36,39 @@ inline mc_status_t launch_fast_one(const RowsArgs& a, cudaStream_t stream, bool 
     return MC_OK;
 }
 
-// R = 1 epilogues (store, argmax)
+// Tile shapes, from a sweep on B200 (graph replay, PDL, rotating weight copies):
+//  * a second register buffer (DB) and early widening (PRE) both cost registers and were
+//    slower than the plain form on every shape tried, so neither is selected here;
+//  * e4m3: two rows per warp share each shared-memory read of x, which is what lifts the
+//    large-N case (lm_head 57 -> 45 us); bf16 is best with one row per warp.
 template <int WB, int PRO, int EPI>
 inline mc_status_t launch_fast_rows(const RowsArgs& a, cudaStream_t stream, bool pdl) {
     const uint32_t per_lane = (a.K * WB / 16u + 31u) / 32u;
     const uint32_t sms = (uint32_t)sm_count();
     if constexpr (WB == 2) {
         if (per_lane <= 9) {
-            if (a.N <= 24u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 768>(a, stream, pdl);
-            return launch_fast_one<2, 1, 9, false, true, PRO, EPI, 512>(a, stream, pdl);   // two rows in flight per warp
+            if (a.N <= 24u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 768>(a, stream, pdl);   // one round
+            return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 1024>(a, stream, pdl);
         }
         if (per_lane <= 24 && a.N <= 16u * sms) return launch_fast_one<2, 1, 24, false, false, PRO, EPI, 512>(a, stream, pdl);
         return launch_fast_one<2, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
     } else {
-        if (per_lane <= 5) {
-            if (a.N <= 24u * sms) return launch_fast_one<1, 1, 5, true, false, PRO, EPI, 768>(a, stream, pdl);
-            return launch_fast_one<1, 1, 5, false, true, PRO, EPI, 1024>(a, stream, pdl);
-        }
+        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, false, PRO, EPI, 1024>(a, stream, pdl);
         if (per_lane <= 12 && a.N <= 16u * sms) return launch_fast_one<1, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
-        return launch_fast_one<1, 1, 6, false, false, PRO, EPI, 1024>(a, stream, pdl);
+        return launch_fast_one<1, 2, 6, false, false, PRO, EPI, 512>(a, stream, pdl);
     }
 }
 
-// R = 2: SwiGLU epilogue over interleaved (gate, up) rows
+// SwiGLU epilogue over interleaved (gate, up) rows: a warp owns a pair
 template <int WB, int PRO>
 inline mc_status_t launch_fast_pairs(const RowsArgs& a, cudaStream_t stream, bool pdl) {
     const uint32_t per_lane = (a.K * WB / 16u + 31u) / 32u;
     if constexpr (WB == 2) {
-        if (per_lane <= 9) return launch_fast_one<2, 2, 9, false, true, PRO, EPI_SWIGLU, 256>(a, stream, pdl);
+        if (per_lane <= 9) return launch_fast_one<2, 2, 9, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
         return launch_fast_one<2, 2, 12, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
     } else {
-        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, true, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
-        return launch_fast_one<1, 2, 6, false, false, PRO, EPI_SWIGLU, 1024>(a, stream, pdl);
+        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, false, PRO, EPI_SWIGLU, 1024>(a, stream, pdl);
+        return launch_fast_one<1, 2, 6, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
     }
 }
 

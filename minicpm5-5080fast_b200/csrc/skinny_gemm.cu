@@ -127,6 +127,9 @@ struct SkinnyArgs {
     uint32_t splits, kb_per_split;   // splits = cluster size along x
     uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
     uint32_t op_stages, raw_stages;  // ring depths (<= 8), chosen by the launcher from the grid size
+#ifdef MCL_TIMELINE
+    unsigned long long* tl;          // [grid][8] globaltimer stamps (development builds only)
+#endif
 };
 
 // swizzled byte offset of 16-byte chunk `cc` (0..7) of tile row `row`
@@ -139,7 +142,7 @@ template <int MODE, int NPAD> struct Ring {
     static constexpr uint32_t A_OP = kTileN * kRowBytes;                         // operand A stage (16 KB)
     static constexpr uint32_t B_OP = NPAD * kRowBytes;                           // operand B stage
     static constexpr uint32_t A_RAW = MODE == SKINNY_W_E4M3 ? kTileN * 64 : 0;   // raw e4m3 stage (8 KB)
-    static constexpr uint32_t bytes(uint32_t ops, uint32_t raws) { return ops * (A_OP + B_OP) + raws * A_RAW; }
+    __host__ __device__ static constexpr uint32_t bytes(uint32_t ops, uint32_t raws) { return ops * (A_OP + B_OP) + raws * A_RAW; }
 };
 
 }  // namespace
@@ -163,7 +166,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
+#ifdef MCL_TIMELINE
+#define MCL_STAMP(i) do { if (a.tl != nullptr) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); a.tl[(size_t)blockIdx.x * 8 + (i)] = t_; } } while (0)
+#else
+#define MCL_STAMP(i) ((void)0)
+#endif
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    if (tid == 0) MCL_STAMP(0);
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = base, sB = base + OPS * G::A_OP, sRaw = sB + OPS * G::B_OP;
     const uint32_t bar0 = smem_u32(bars);
@@ -202,6 +211,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // every CTA of the cluster is running before anyone addresses a peer's shared memory
+    asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+    asm volatile("barrier.cluster.wait;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     volatile int* abortp = &abort_flag;
 
@@ -218,8 +230,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mbar_expect_tx(bar, W_BYTES + (E4 ? 0u : G::B_OP));
                 tma_load_2d((E4 ? sRaw : sA) + it * W_BYTES, &map_w, bar, (int32_t)((kb0 + it) * BK), n0);
             }
+            MCL_STAMP(1);
             pdl_trigger();
             pdl_wait();
+            MCL_STAMP(2);
             bool ok = true;
             uint32_t itx = 0;   // next X stage to issue
             auto issue_x = [&](uint32_t it) {
@@ -273,6 +287,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mma_commit(op_empty(s));      // frees the stage once the MMAs have read it
             }
             if (ok && nloc > 0) mma_commit(accum_bar);
+            MCL_STAMP(3);
         }
     } else if constexpr (E4) {
         // ---------------------------------------------------------------- e4m3 -> bf16 widening
@@ -312,13 +327,26 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
 
     // ---------------------------------------------------------------------- epilogue
-    // (1) accumulator -> this CTA's shared memory, red[m][n_local] fp32 (the ring is free:
-    //     every MMA that read it has completed once accum_bar fires)
-    float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
+    // The tile's 128 features are cut into S contiguous slices, one per CTA of the cluster.
+    // (1) every CTA PUSHES its partial accumulator rows into the owner's shared memory
+    //     (part[rank][feature][m], a region of its own behind the ring, so a push can never land
+    //     in memory the owner's pipeline still uses): a thread holds 16 consecutive m of one
+    //     feature after tcgen05.ld, i.e. 64 contiguous bytes = four 16-byte remote stores;
+    // (2) one cluster barrier;
+    // (3) each owner sums its S partials from its own shared memory in rank order, scales, stores.
+    // Nothing remote is touched after the barrier, so no CTA waits for its peers before it exits.
+    const uint32_t S = a.splits, rank = split;
+    const uint32_t per_n = kTileN / S;                               // features per owner (S divides 128)
+    constexpr uint32_t PITCH = NPAD + 4;                             // fp32 per feature row: 16-byte aligned pushes, spread banks
+    const uint32_t part_s = base + G::bytes(OPS, E4 ? RAWS : 0);     // part[S][per_n][PITCH] fp32
     if (warp >= 2 && warp < 6) {
         const uint32_t q = warp & 3u;       // the TMEM lane quarter this warp may read
         const bool ok = nloc > 0 && mbar_wait(accum_bar, 0u, abortp);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t nl = q * 32u + lane, owner = nl / per_n;
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                     : "r"(part_s + ((rank * per_n + (nl - owner * per_n)) * PITCH) * 4u), "r"(owner));
 #pragma unroll
         for (int c0 = 0; c0 < NPAD; c0 += 16) {
             uint32_t r[16];
@@ -335,67 +363,55 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) red[(c0 + j) * kTileN + q * 32u + lane] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; j += 4)
+                asm volatile("st.shared::cluster.v4.u32 [%0], {%1,%2,%3,%4};"
+                             ::"r"(remote + (uint32_t)(c0 + j) * 4u), "r"(r[j]), "r"(r[j + 1]), "r"(r[j + 2]), "r"(r[j + 3]) : "memory");
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
-    // (2) every CTA of the cluster has published its partial tile
+    if (tid == 64) MCL_STAMP(4);
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-    // (3) this CTA finishes a contiguous slice of the tile: fixed rank order over the cluster.
-    //     Four consecutive features per thread and step; the (up to 8) remote reads of a
-    //     step are issued together, then summed in rank order.
+    if (tid == 0) MCL_STAMP(5);
     {
-        const uint32_t S = a.splits, rank = split;
-        const uint32_t red_s = smem_u32(red);
         const bool failed = *abortp != 0;
-        const uint32_t total = a.M * (kTileN / 4);                 // float4 units
-        const uint32_t per = (total + S - 1) / S, lo = rank * per, hi = min(total, lo + per);
-        for (uint32_t e = lo + tid; e < hi; e += kThreads) {
-            const uint32_t m = e / (kTileN / 4), nl = (e % (kTileN / 4)) * 4u, n = (uint32_t)n0 + nl;
-            float4 v[8];
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r) {
-                v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r < S) {
-                    uint32_t ra;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_s + 16u * e), "r"(r));
-                    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-                                 : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w) : "r"(ra) : "memory");
+        const uint32_t nbase = (uint32_t)n0 + rank * per_n;          // first feature this CTA finishes
+        auto partial_sum = [&](uint32_t n_rel, uint32_t m) {
+            float acc = 0.f;
+            for (uint32_t r = 0; r < S; ++r) {    // rank order: bit-reproducible
+                float v;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(part_s + ((r * per_n + n_rel) * PITCH + m) * 4u) : "memory");
+                acc += v;
+            }
+            return acc;
+        };
+        if (!a.swiglu) {
+            for (uint32_t idx = tid; idx < per_n * a.M; idx += kThreads) {
+                const uint32_t m = idx / per_n, n_rel = idx % per_n, n = nbase + n_rel;   // n fastest: coalesced stores
+                float acc = partial_sum(n_rel, m);
+                if (n < a.N && !failed) {
+                    if (a.w_scale != nullptr) acc *= a.w_scale[n];
+                    if (MODE == SKINNY_W8A8) acc *= a.x_scale[m];
+                    a.y[(size_t)m * a.N + n] = f32_to_bf16_bits(acc);
                 }
             }
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r)
-                if (r < S) { acc[0] += v[r].x; acc[1] += v[r].y; acc[2] += v[r].z; acc[3] += v[r].w; }
-            if (failed) continue;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (n + j < a.N) {
-                    if (a.w_scale != nullptr) acc[j] *= a.w_scale[n + j];
-                    if (MODE == SKINNY_W8A8) acc[j] *= a.x_scale[m];
-                }
-            }
-            if (!a.swiglu) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (n + j < a.N) a.y[(size_t)m * a.N + n + j] = f32_to_bf16_bits(acc[j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; j += 2) {
-                    if (n + j + 1 < a.N) {
-                        const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(acc[j]) << 16);
-                        const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(acc[j + 1]) << 16);
-                        a.y[(size_t)m * (a.N / 2u) + ((n + j) >> 1)] = f32_to_bf16_bits(swiglu_f32(gb, ub));
-                    }
+        } else {
+            for (uint32_t idx = tid; idx < (per_n / 2u) * a.M; idx += kThreads) {
+                const uint32_t m = idx / (per_n / 2u), p = idx % (per_n / 2u), n = nbase + 2u * p;
+                float gt = partial_sum(2u * p, m), up = partial_sum(2u * p + 1u, m);
+                if (n + 1 < a.N && !failed) {
+                    if (a.w_scale != nullptr) { gt *= a.w_scale[n]; up *= a.w_scale[n + 1]; }
+                    if (MODE == SKINNY_W8A8) { gt *= a.x_scale[m]; up *= a.x_scale[m]; }
+                    const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(gt) << 16);
+                    const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
+                    a.y[(size_t)m * (a.N / 2u) + (n >> 1)] = f32_to_bf16_bits(swiglu_f32(gb, ub));
                 }
             }
         }
     }
-    // (4) nobody leaves while a peer may still read its shared memory
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    if (tid == 0) MCL_STAMP(6);
     __syncthreads();
+    if (tid == 0) MCL_STAMP(7);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -465,7 +481,6 @@ mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t 
 template <int MODE, int NPAD>
 mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
     using G = Ring<MODE, NPAD>;
-    static_assert((size_t)NPAD * kTileN * 4 <= (size_t)G::bytes(3, 0), "reduce tile must fit in the ring");
     auto kern = skinny_gemm_kernel<MODE, NPAD>;
     constexpr size_t smem_max = 112u * 1024u;
     static bool attr_done = false;
@@ -477,7 +492,7 @@ mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32
         }
         attr_done = true;
     }
-    const size_t smem = (size_t)G::bytes(a.op_stages, MODE == SKINNY_W_E4M3 ? a.raw_stages : 0) + 1024;
+    const size_t smem = (size_t)G::bytes(a.op_stages, MODE == SKINNY_W_E4M3 ? a.raw_stages : 0) + (size_t)(NPAD + 4) * kTileN * 4 + 2048;
     CUtensorMap map_w, map_x;
     mc_status_t s;
     if (MODE == SKINNY_W_BF16) {
@@ -543,14 +558,18 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
     // kernel's CTA can then no longer become resident (and prefetch its weights) while this
     // one drains.
     const uint32_t npad = M <= 16 ? 16u : (M <= 32 ? 32u : 64u);
-    const uint32_t op_stage = (uint32_t)(kTileN + npad) * kRowBytes, budget = 108u * 1024u;
+    const uint32_t op_stage = (uint32_t)(kTileN + npad) * kRowBytes;
+    const uint32_t budget = 108u * 1024u - (npad + 4u) * kTileN * 4u - 1024u;  // minus the split-K exchange region
     if (mode == SKINNY_W_E4M3) {
-        a.op_stages = 3u;
-        a.raw_stages = (budget - 3u * op_stage) / (kTileN * 64u);
+        // operand ring of 3 (2 when the raw ring would otherwise drop below 2 stages)
+        a.op_stages = (budget >= 3u * op_stage + 2u * kTileN * 64u) ? 3u : 2u;
+        a.raw_stages = (budget - a.op_stages * op_stage) / (kTileN * 64u);
         if (a.raw_stages > 8u) a.raw_stages = 8u;
+        if (a.raw_stages < 2u) a.raw_stages = 2u;
     } else {
         a.op_stages = budget / op_stage;
         if (a.op_stages > 8u) a.op_stages = 8u;
+        if (a.op_stages < 2u) a.op_stages = 2u;
         a.raw_stages = 1u;
     }
     if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(w, x, a, grid, stream, pdl);

@@ -422,3 +422,26 @@ def test_residual_rmsnorm_rows(pkg, g):
     want_res = onp.add_bf16(res, add)
     assert np.array_equal(g.host_u16(dres), want_res)
     check_close(g.host_u16(dout), onp.rmsnorm_bf16(nw, want_res), what="residual_rmsnorm_rows")
+
+
+# ---- peer all-gather kernel on one GPU: self exchange, and the bounded wait running out ---------
+def test_peer_allgather_single_rank_and_timeout(pkg, g):
+    per = 64                                             # bf16 elements per slot
+    shard = g.dev(onp.seeded_bf16(190, (per,), 1.0))
+    full = torch.zeros(2 * per, dtype=torch.int16, device="cuda")
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bufs = torch.tensor([full.data_ptr()], dtype=torch.int64, device="cuda")
+    fl = torch.tensor([flags.data_ptr()], dtype=torch.int64, device="cuda")
+    for k in range(3):                                   # world of one: push to myself, see my own flag
+        pkg.peer_allgather(shard, per * 2, per * 2, bufs, fl, flags, epoch, 0, 1, status=status)
+    g.sync()
+    assert torch.equal(full[:per], shard) and epoch.item() == 3 and flags[0].item() == 3 and status.item() == 0
+    # a "world" of two whose second rank never signals: the wait must give up and report it
+    bufs2 = torch.tensor([full.data_ptr(), full.data_ptr()], dtype=torch.int64, device="cuda")
+    fl2 = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64, device="cuda")
+    pkg.peer_allgather(shard, per * 2, per * 2, bufs2, fl2, flags, epoch, 0, 2, timeout_ns=2_000_000, status=status)
+    g.sync()
+    assert status.item() == 1 and epoch.item() == 4      # gave up after ~2 ms, context still healthy
+    assert torch.equal(full[:per], shard)
