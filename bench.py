@@ -234,11 +234,15 @@ class Stream:
         self.layers = []
         self.handle = None
         self.desc = None
-        if world == 1:
-            # one GPU: the weights live in the library's own arena layout and the step is the
-            # library's decode-stack object (C ABI); the per-call launch sequence below is kept
-            # for the sharded runs
-            self.desc = pkg.stack_desc(L, H, QKV, I, V, fp8=self.fp8, max_batch=max(m, 1), graph=True)
+        # MC_GATHER: "fused" (default) = the library's sharded stack, outputs exchanged inside the GEMV
+        # kernels; "peer" = per-call launches + the library's peer all-gather kernel; "nccl" = per-call
+        # launches + ncclAllGather.  The last two are kept as comparison arms.
+        self.gather_mode = os.environ.get("MC_GATHER", "fused") if world > 1 else None
+        if world == 1 or (m == 1 and self.gather_mode == "fused"):
+            # the weights live in the library's own arena layout (this rank's shard of it) and the
+            # step is the library's decode-stack object (C ABI)
+            self.desc = pkg.stack_desc(L, H, QKV, I, V, fp8=self.fp8, max_batch=max(m, 1), graph=True,
+                                       world=world, rank=rank)
             wbytes, sbytes = pkg.stack_sizes(self.desc)
             self.arena = torch.zeros(wbytes, dtype=torch.uint8, device=dev)
             self.scratch = torch.zeros(sbytes, dtype=torch.uint8, device=dev)
@@ -291,6 +295,15 @@ class Stream:
         self.nf = place(0, "final_norm", bf16_bits(1.0 + 0.1 * torch.randn(H, generator=g, device=dev)))
         if self.desc is not None:
             self.handle = pkg.stack_create(self.desc, self.arena, self.scratch)
+            if world > 1:
+                # exchange region in symmetric (peer-mapped) memory, same size on every rank
+                import torch.distributed._symmetric_memory as symm
+                self.region = symm.empty(pkg.stack_exchange_bytes(self.desc), dtype=torch.uint8, device=dev)
+                self.region.zero_()
+                hnd = symm.rendezvous(self.region, dist.group.WORLD)
+                pkg.stack_bind_exchange(self.handle, [int(p) for p in hnd.buffer_ptrs])
+                torch.cuda.synchronize()
+                dist.barrier()
         z = lambda *s: torch.zeros(s, dtype=torch.int16, device=dev)
         self.per = {"qkv": shard_rows(QKV, world, 0)[2], "o": shard_rows(H, world, 0)[2],
                     "mid": shard_rows(I, world, 0)[2], "down": shard_rows(H, world, 0)[2]}
@@ -307,7 +320,7 @@ class Stream:
         self.pair = torch.zeros((world, m, 2), dtype=torch.float32, device=dev)
         self.launches = 0
         self.peer = None
-        if world > 1 and m == 1 and os.environ.get("MC_GATHER", "peer") == "peer":
+        if world > 1 and m == 1 and self.gather_mode == "peer":
             try:
                 self._setup_peer(dev)
             except Exception as e:      # no symmetric memory on this stack: NCCL all-gather, same kernels otherwise
@@ -409,7 +422,7 @@ class Stream:
         """One GPU: the whole step through the C ABI's decode-stack object."""
         m = self.m
         self.pkg.stack_step(self.handle, self.x_in, m, self.tok)
-        self.launches = (4 * L + 2) if m == 1 else (6 * L + 1 + (2 if m <= 4 else 3))
+        self.launches = (4 * L + 2 + (1 if self.world > 1 else 0)) if m == 1 else (6 * L + 1 + (2 if m <= 4 else 3))
         return self.tok
 
     def step(self, pdl=True):
@@ -543,6 +556,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     with torch.cuda.stream(stream), ClockSampler(local) as clk:
+        barrier()                                   # sharded kernels wait (bounded) for their peers: start together
         st.step()                                   # eager once: sets attributes, warms NCCL
         stream.synchronize()
         graph, mode = None, "eager+pdl"
@@ -557,6 +571,7 @@ def run_ours(args):
                 torch.cuda.synchronize()
         run = (lambda: graph.replay()) if graph is not None else (lambda: st.step())
 
+        barrier()
         for _ in range(max(args.warmup, 3)):
             run()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -584,6 +599,7 @@ def run_ours(args):
                 run()
                 hres.copy_(res_dev, non_blocking=True)
                 stream.synchronize()
+        barrier()
         for _ in range(3):
             e2e_step()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -597,6 +613,8 @@ def run_ours(args):
 
     if getattr(st, "peer", None) is not None and int(st.peer["status"].item()) != 0:
         raise SystemExit("bench: a bounded wait of the peer all-gather kernel ran out (a rank fell behind or died)")
+    if not single and world > 1 and st.handle is not None and pkg.stack_exchange_status(st.handle, stream) != 0:
+        raise SystemExit("bench: a bounded wait of the sharded stack ran out (a rank fell behind or died)")
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -618,8 +636,10 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if wb == 2 else "fp8_e4m3_weight_only(fp32 acc)",
             "data": "synthetic",
             "config": {"workload": workload_name(args), "launch": mode, "parallelism": f"N-sharded x{world}",
-                       "gather": (None if world == 1 else ("peer-store kernel over NVLink (symmetric memory)" if getattr(st, "peer", None)
-                                  else "nccl all_gather" + (" (" + getattr(st, "peer_error", "") + ")" if getattr(st, "peer_error", "") else ""))),
+                       "gather": (None if world == 1 else
+                                  "inside the GEMV kernels: peer stores + arrival counters over NVLink (symmetric memory)" if st.handle is not None else
+                                  "peer-store kernel over NVLink (symmetric memory)" if getattr(st, "peer", None) else
+                                  "nccl all_gather" + (" (" + getattr(st, "peer_error", "") + ")" if getattr(st, "peer_error", "") else "")),
                        "l2": ("every call reads a different weight copy; the copies together exceed twice the L2" if single
                               else "inputs larger than L2: every step streams its own weights from HBM once"),
                        "bytes_per_step": total_bytes, "calls_per_step": st.launches if not single else st.copies,
@@ -631,7 +651,8 @@ def run_ours(args):
             "clocks": clk.summary(),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_kind": f"{peak_kind} copy bandwidth", "frac_of_nominal_8TBs": per_gpu / NOMINAL_HBM_GBS,
-                         "kernel": "gemv_rows_kernel (all launches of the step)", "traffic": None},
+                         "kernel": ("gemv_fast_kernel" if args.m == 1 else "skinny_gemm_kernel" if args.m > 4 else "gemv_rows_kernel")
+                         + " (whole step: every launch of the chain)", "traffic": None},
         }
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}

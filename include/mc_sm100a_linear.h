@@ -300,7 +300,8 @@ typedef struct mc_sm100_stack_desc_t {
     uint32_t max_batch;          /* 1..64 */
     float    eps;
     uint32_t enable_cuda_graph;
-    uint32_t reserved[4];        /* must be zero */
+    uint32_t world, rank;        /* N-sharding over the GPUs of one node: world 0 or 1 = one GPU, else 2..8 */
+    uint32_t reserved[2];        /* must be zero */
 } mc_sm100_stack_desc_t;
 
 typedef struct mc_sm100_stack* mc_sm100_stack_t;
@@ -338,6 +339,24 @@ MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const 
 
 /* --------------------------------------------------------------- multi-GPU --- */
 
+/* Sharded stack (desc.world > 1, M = 1 only).  layers/hidden/qkv_rows/inter/vocab describe the WHOLE
+ * model; every linear is split along its output rows (gate_up by (gate, up) pairs, lm_head by
+ * vocab) with a uniform pitch of ceil(rows / world) rounded up to 8, rank r owning rows
+ * [r*pitch, min(rows, (r+1)*pitch)); mc_sm100_stack_sizes / _section then describe THIS rank's
+ * arena (norm weights whole).  Outputs travel between ranks inside the GEMV kernels
+ * (mc_sm100_gemv_sharded) as tagged words, through an exchange region that every rank allocates in peer-mappable
+ * memory (same size everywhere) and whose addresses, as mapped in this process, are bound once:
+ *   mc_sm100_stack_exchange_bytes(desc, &n); allocate + map n bytes on every rank;
+ *   mc_sm100_stack_bind_exchange(stack, addrs (host array [world], [rank] = own), stream);
+ *   barrier across ranks; then every rank calls the same sequence of steps.
+ * bind zeroes this rank's region.  mc_sm100_stack_exchange_status reads (and keeps) the
+ * sticky failure word: 0 = every wait so far was satisfied, 1 = a wait ran out (a peer is gone
+ * or out of step): the outputs of that step are undefined and the stack must be re-bound. */
+MC_SM100_API mc_status_t mc_sm100_stack_exchange_bytes(const mc_sm100_stack_desc_t* desc, uint64_t* bytes);
+MC_SM100_API mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t stack, const uint64_t* h_peer_addrs,
+                                                      uint64_t timeout_ns, void* stream);
+MC_SM100_API mc_status_t mc_sm100_stack_exchange_status(mc_sm100_stack_t stack, int32_t* h_status, void* stream);
+
 /* All-gather of an N-shard over NVLink peer memory in one small kernel (no counterpart in
  * the reference, which is single-GPU; native/include/minicpm_runtime.h:61).  Rank `rank`
  * stores its slice (shard_bytes, a multiple of 16) at offset rank * slot_bytes of EVERY
@@ -352,6 +371,60 @@ MC_SM100_API mc_status_t mc_sm100_peer_allgather(const void* d_shard, uint32_t s
                                                  uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank,
                                                  uint32_t world, uint64_t timeout_ns, int32_t* d_status,
                                                  void* stream, int32_t pdl);
+
+/* Sharded M = 1 linear with the output exchange INSIDE the GEMV kernel (no counterpart in
+ * the reference, which is single-GPU).  A gathered vector is an array of uint32 words, one per
+ * element: bf16 bits in the low half, the low 16 bits of the exchange's sequence number in the
+ * high half.  The producing kernel stores each output word straight into slot `rank` of every
+ * rank's gathered vector (out_peer[p], peer-mapped, plain 32-bit stores); the consuming kernel
+ * polls the words it needs -- bounded, timeout_ns, 0 = 1 s -- until every tag is the expected
+ * one.  No flags, fences or atomics.  Sequence numbers are (*d_step - 1) * seq_mul + seq_add.
+ * A wait that runs out sets *d_status = 1, after which all later waits give up at once. */
+typedef struct mc_sm100_shard_io_t {
+    uint32_t struct_size;          /* sizeof(mc_sm100_shard_io_t) */
+    uint32_t world, rank;          /* world 2..8 */
+    uint32_t in_tagged;            /* 1: d_x (prologue 0) / d_addend (prologue 1) is a tagged gathered vector */
+    uint32_t in_seq_mul, in_seq_add;
+    uint32_t out_slot;             /* slot pitch of the gathered output in words; 0 = output stays local (d_y, bf16) */
+    uint32_t out_seq_mul, out_seq_add;
+    uint32_t reserved;
+    const uint32_t* d_step;        /* device word >= 1 */
+    int32_t* d_status;
+    uint64_t timeout_ns;
+    uint64_t out_peer[8];
+} mc_sm100_shard_io_t;
+
+/* prologue: 0 = x is d_x; 1 = residual add + RMSNorm (d_x = residual in, d_addend may be NULL,
+ * d_norm_w, d_res_out as in mc_sm100_gemv_rows_prologue).  epilogue: 0 = store, 1 = SwiGLU over
+ * interleaved (gate, up) rows (N even, N/2 outputs).  d_scale NULL = bf16 weights, else e4m3.
+ * d_y is used only when io->out_slot == 0.  N = rows of THIS rank's shard. */
+MC_SM100_API mc_status_t mc_sm100_gemv_sharded(int32_t prologue, int32_t epilogue, const void* d_w,
+                                               const float* d_scale, const uint16_t* d_x,
+                                               const uint16_t* d_addend, const uint16_t* d_norm_w,
+                                               uint16_t* d_res_out, uint16_t* d_y, uint32_t N, uint32_t K,
+                                               float eps, const mc_sm100_shard_io_t* io, void* stream,
+                                               int32_t pdl);
+
+/* mc_sm100_lm_head_argmax_prologue over this rank's vocab shard (N rows, global index of row 0 =
+ * index_base) whose addend is a tagged gathered vector (io->in_tagged = 1).  Logits and the
+ * (value, index) of the shard stay local; mc_sm100_peer_argmax reduces them across ranks. */
+MC_SM100_API mc_status_t mc_sm100_lm_head_argmax_sharded(
+    const void* d_w, const float* d_scale, const uint16_t* d_res_in, const uint16_t* d_addend,
+    const uint16_t* d_norm_w, uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n, float eps,
+    int32_t index_base, void* d_stage, int32_t* d_out_idx, float* d_out_val, const mc_sm100_shard_io_t* io,
+    void* stream, int32_t pdl);
+
+/* Greedy token over vocab shards in one single-CTA kernel: pushes this rank's (value, index)
+ * to every rank (d_pair_peers: device array of `world` addresses of each rank's [world] x 8-byte
+ * pair slots), signals, waits (bounded) for all ranks' pairs of step *d_step, reduces with the
+ * reference's tie rule (lowest index, native/kernels/sm120/sampling.cu:26, 80), writes the token
+ * and the value, and finally advances *d_step. */
+MC_SM100_API mc_status_t mc_sm100_peer_argmax(const float* d_val, const int32_t* d_idx,
+                                              const uint64_t* d_pair_peers, const uint64_t* d_flag_peers,
+                                              const uint64_t* d_my_pairs, const uint32_t* d_my_flags,
+                                              uint32_t* d_step, uint32_t rank, uint32_t world,
+                                              uint64_t timeout_ns, int32_t* d_status, int32_t* d_token,
+                                              float* d_token_val, void* stream, int32_t pdl);
 
 /* ------------------------------------------------------------ packed weights --- */
 

@@ -65,6 +65,13 @@ SIGNATURES = {
     "mc_sm100_stack_logits": (_vp, [_vp]),
     "mc_sm100_stack_step": (_i32, [_vp, _vp, _u32, _vp, _vp]),
     "mc_sm100_stack_step_host": (_i32, [_vp, _vp, _u32, _vp, _vp]),
+    "mc_sm100_stack_exchange_bytes": (_i32, [_vp, C.POINTER(C.c_uint64)]),
+    "mc_sm100_stack_bind_exchange": (_i32, [_vp, _vp, C.c_uint64, _vp]),
+    "mc_sm100_stack_exchange_status": (_i32, [_vp, C.POINTER(_i32), _vp]),
+    "mc_sm100_gemv_sharded": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _vp, _i32]),
+    "mc_sm100_lm_head_argmax_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _i32,
+                                               _vp, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_peer_argmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_peer_allgather": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _i32]),
     "mc_sm100_wpk_name_hash": (C.c_uint64, [C.c_char_p]),
     "mc_sm100_wpk_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
@@ -114,7 +121,9 @@ def _check(status: int) -> None:
 
 def _p(t) -> int | None:
     """Device (or pinned host) address of a tensor, None passes NULL."""
-    return None if t is None else t.data_ptr()
+    if t is None:
+        return None
+    return int(t) if isinstance(t, int) else t.data_ptr()
 
 
 def _stream(stream) -> int | None:
@@ -251,15 +260,17 @@ def debug_take_error() -> int:
 class StackDesc(C.Structure):
     _fields_ = [("struct_size", _u32), ("layers", _u32), ("hidden", _u32), ("qkv_rows", _u32), ("inter", _u32),
                 ("vocab", _u32), ("precision", _u32), ("max_batch", _u32), ("eps", C.c_float),
-                ("enable_cuda_graph", _u32), ("reserved", _u32 * 4)]
+                ("enable_cuda_graph", _u32), ("world", _u32), ("rank", _u32), ("reserved", _u32 * 2)]
 
 
 SEC = {"qkv": 0, "o": 1, "gate_up": 2, "down": 3, "norm1": 4, "norm2": 5, "qkv_scale": 6, "o_scale": 7,
        "gate_up_scale": 8, "down_scale": 9, "lm_head": 10, "final_norm": 11, "lm_head_scale": 12}
 
 
-def stack_desc(layers, hidden, qkv_rows, inter, vocab, fp8=False, max_batch=1, eps=1e-6, graph=True) -> StackDesc:
+def stack_desc(layers, hidden, qkv_rows, inter, vocab, fp8=False, max_batch=1, eps=1e-6, graph=True,
+               world=1, rank=0) -> StackDesc:
     d = StackDesc()
+    d.world, d.rank = (world if world > 1 else 0), rank
     d.struct_size = C.sizeof(StackDesc)
     d.layers, d.hidden, d.qkv_rows, d.inter, d.vocab = layers, hidden, qkv_rows, inter, vocab
     d.precision, d.max_batch, d.eps, d.enable_cuda_graph = (2 if fp8 else 0), max_batch, eps, int(graph)
@@ -299,6 +310,65 @@ def stack_step_host(handle, h_x, M, h_tokens, stream=None):
 
 def stack_logits_ptr(handle) -> int:
     return lib().mc_sm100_stack_logits(handle)
+
+
+def stack_exchange_bytes(desc) -> int:
+    n = C.c_uint64()
+    _check(lib().mc_sm100_stack_exchange_bytes(C.byref(desc), C.byref(n)))
+    return n.value
+
+
+def stack_bind_exchange(handle, peer_addrs, timeout_ns=0, stream=None):
+    arr = (C.c_uint64 * len(peer_addrs))(*[int(a) for a in peer_addrs])
+    _check(lib().mc_sm100_stack_bind_exchange(handle, C.cast(arr, _vp), timeout_ns, _stream(stream)))
+
+
+def stack_exchange_status(handle, stream=None) -> int:
+    v = _i32()
+    _check(lib().mc_sm100_stack_exchange_status(handle, C.byref(v), _stream(stream)))
+    return v.value
+
+
+# ---- sharded linears (exchange inside the GEMV) -------------------------------------------------
+class ShardIO(C.Structure):
+    _fields_ = [("struct_size", _u32), ("world", _u32), ("rank", _u32), ("in_tagged", _u32), ("in_seq_mul", _u32),
+                ("in_seq_add", _u32), ("out_slot", _u32), ("out_seq_mul", _u32), ("out_seq_add", _u32), ("reserved", _u32),
+                ("d_step", _vp), ("d_status", _vp), ("timeout_ns", C.c_uint64), ("out_peer", C.c_uint64 * 8)]
+
+
+def shard_io(world, rank, step, status, in_seq=None, out_slot=0, out_seq=None, out_peer=(), timeout_ns=0) -> ShardIO:
+    """step/status: device tensors (or addresses); in_seq/out_seq: (mul, add) of the consumed / produced
+    exchange, None = local input / local output; out_peer: address of every rank's gathered vector."""
+    io = ShardIO()
+    io.struct_size = C.sizeof(ShardIO)
+    io.world, io.rank, io.out_slot = world, rank, out_slot
+    if in_seq is not None:
+        io.in_tagged, io.in_seq_mul, io.in_seq_add = 1, in_seq[0], in_seq[1]
+    if out_seq is not None:
+        io.out_seq_mul, io.out_seq_add = out_seq
+    io.d_step, io.d_status, io.timeout_ns = _p(step), _p(status), timeout_ns
+    for i, a in enumerate(out_peer):
+        io.out_peer[i] = int(a)
+    return io
+
+
+def gemv_sharded(prologue, epilogue, w, scale, x, addend, norm_w, res_out, y, N, K, eps, io, stream=None, pdl=False):
+    _check(lib().mc_sm100_gemv_sharded(prologue, epilogue, _p(w), _p(scale), _p(x), _p(addend), _p(norm_w), _p(res_out),
+                                       _p(y), N, K, eps, C.cast(C.byref(io), _vp), _stream(stream), int(pdl)))
+
+
+def lm_head_argmax_sharded(w, scale, res_in, addend, norm_w, res_out, logits, N, n, eps, index_base, stage, out_idx,
+                           out_val, io, stream=None, pdl=False):
+    _check(lib().mc_sm100_lm_head_argmax_sharded(_p(w), _p(scale), _p(res_in), _p(addend), _p(norm_w), _p(res_out),
+                                                 _p(logits), N, n, eps, index_base, _p(stage), _p(out_idx), _p(out_val),
+                                                 C.cast(C.byref(io), _vp), _stream(stream), int(pdl)))
+
+
+def peer_argmax(val, idx, pair_peers, flag_peers, my_pairs, my_flags, step, rank, world, status, token, token_val=None,
+                timeout_ns=0, stream=None, pdl=False):
+    _check(lib().mc_sm100_peer_argmax(_p(val), _p(idx), _p(pair_peers), _p(flag_peers), _p(my_pairs), _p(my_flags),
+                                      _p(step), rank, world, timeout_ns, _p(status), _p(token), _p(token_val),
+                                      _stream(stream), int(pdl)))
 
 
 # ---- packed weight file -----------------------------------------------------------------------

@@ -47,6 +47,59 @@ inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
         }                                                                        \
     } while (0)
 
+// ---- exchange of N-sharded outputs between the GPUs of one node ----------------
+// A sharded linear stores each output element straight into EVERY rank's gathered vector
+// (peer-mapped addresses) as one 32-bit word: bf16 bits in the low half, the low 16 bits of
+// the exchange's sequence number in the high half.  A 32-bit store is atomic, so the word
+// carries its own "valid" mark: the consumer polls the words it needs until every tag is the
+// expected one -- no flag, no fence, no atomic on the critical path; the cost of an exchange
+// is one NVLink store latency.  Every slot of a vector is rewritten by every exchange, so a
+// slot only ever holds the current or the previous exchange's tag.  All zero = not sharded.
+struct ShardIO {
+    const uint32_t* step;       // device word, >= 1: index of the running step
+    int32_t* status;            // set to 1 when a wait ran out (sticky: later waits give up at once)
+    uint64_t timeout_ns;
+    uint64_t out_peer[8];       // rank p's gathered output vector (uint32 words) as mapped here ([rank] = own)
+    uint32_t world, rank;
+    uint32_t in_tagged;         // 1: the activation (PRO_NONE) / the addend (PRO_RESNORM) is a tagged gathered vector
+    uint32_t in_seq_mul, in_seq_add;     // its sequence number = (*step - 1) * in_seq_mul + in_seq_add
+    uint32_t out_slot;          // this rank's outputs start at word rank * out_slot; 0 = outputs stay local (bf16)
+    uint32_t out_seq_mul, out_seq_add;
+};
+
+constexpr unsigned long long kShardWaitDefaultNs = 1000ull * 1000ull * 1000ull;   // 1 s
+
+// Checks a caller's exchange descriptor and fills the kernel-side form.  `outs` = output
+// elements this rank produces; push = false for kernels whose output stays local.
+inline mc_status_t shard_io_to_args(const char* who, const mc_sm100_shard_io_t* io, uint32_t outs, bool push, ShardIO& sh) {
+    if (io == nullptr || io->struct_size != sizeof(mc_sm100_shard_io_t) || io->world < 2u || io->world > 8u ||
+        io->rank >= io->world || io->d_step == nullptr || io->d_status == nullptr ||
+        (io->in_tagged != 0u && io->in_seq_mul == 0u && io->in_seq_add == 0u)) {
+        set_error("%s: invalid exchange descriptor", who);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    sh = ShardIO{};
+    sh.step = io->d_step; sh.status = io->d_status;
+    sh.timeout_ns = io->timeout_ns ? io->timeout_ns : kShardWaitDefaultNs;
+    sh.in_tagged = io->in_tagged ? 1u : 0u; sh.in_seq_mul = io->in_seq_mul; sh.in_seq_add = io->in_seq_add;
+    sh.world = io->world; sh.rank = io->rank;
+    if (push && io->out_slot != 0) {
+        if (outs > io->out_slot || (io->out_seq_mul == 0u && io->out_seq_add == 0u)) {
+            set_error("%s: %u outputs do not fit a slot of %u, or no output sequence number", who, outs, io->out_slot);
+            return MC_E_INVALID_ARGUMENT;
+        }
+        for (uint32_t p = 0; p < io->world; ++p) {
+            if (io->out_peer[p] == 0 || (io->out_peer[p] & 3u) != 0) {
+                set_error("%s: peer %u has no output vector", who, p);
+                return MC_E_INVALID_ARGUMENT;
+            }
+            sh.out_peer[p] = io->out_peer[p];
+        }
+        sh.out_slot = io->out_slot; sh.out_seq_mul = io->out_seq_mul; sh.out_seq_add = io->out_seq_add;
+    }
+    return MC_OK;
+}
+
 #if defined(__CUDACC__)
 
 // ---- programmatic dependent launch ----
@@ -129,6 +182,39 @@ __device__ __forceinline__ float warp_sum(float v) {
 // silu(g)*u with the reference's formula g/(1+expf(-g)) (swiglu.cu:66-69).
 __device__ __forceinline__ float swiglu_f32(float g, float u) {
     return (g / (1.0f + expf(-g))) * u;
+}
+
+// ---- sharded exchange, device side ----
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t shard_tag(const ShardIO& s, uint32_t mul, uint32_t add) {
+    return ((*s.step - 1u) * mul + add) & 0xFFFFu;
+}
+
+// Eight consecutive elements (32 bytes, 16-byte aligned) of a tagged gathered vector, read
+// past L1 until every word carries `tag`.  The wait is bounded: after timeout_ns, or as soon
+// as an earlier wait has failed, it records the failure and returns what is there.
+__device__ __forceinline__ void ld_tagged8(const uint32_t* src, uint32_t tag, const ShardIO& s, uint16_t (&bits)[8]) {
+    uint64_t t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        uint32_t w[8];
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(src) : "memory");
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(src + 4) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { ok = ok && (w[j] >> 16) == tag; bits[j] = (uint16_t)(w[j] & 0xFFFFu); }
+        if (ok) return;
+        if ((spins & 31u) == 0u) {
+            if (*reinterpret_cast<volatile int32_t*>(s.status) != 0) return;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > s.timeout_ns) { *reinterpret_cast<volatile int32_t*>(s.status) = 1; return; }
+        }
+    }
 }
 
 #endif  // __CUDACC__

@@ -200,6 +200,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
     }
     pdl_trigger();
     pdl_wait();
+    // sharded run: the activation (or the addend of the prologue) is a vector gathered from all
+    // ranks, one tagged 32-bit word per element; staging polls the words until they are current
+    const bool tagged = a.sh.in_tagged != 0u;
+    const uint32_t in_tag = tagged ? shard_tag(a.sh, a.sh.in_seq_mul, a.sh.in_seq_add) : 0u;
 
     // ---- activation: global -> (prologue) -> shared, eight elements per thread and step ----
     bool inexact = false;
@@ -207,7 +211,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
     if constexpr (PRO == PRO_NONE) {
         for (uint32_t c = threadIdx.x; c < nchunk; c += THREADS) {
             uint16_t bits[8];
-            unpack8(reinterpret_cast<const uint4*>(a.x)[c], bits);
+            if (tagged) ld_tagged8(reinterpret_cast<const uint32_t*>(a.x) + 8u * c, in_tag, a.sh, bits);
+            else unpack8(reinterpret_cast<const uint4*>(a.x)[c], bits);
             put_x8<WB>(xh, xb, c, bits, inexact);
         }
     } else if constexpr (PRO == PRO_RESNORM) {
@@ -216,7 +221,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
         for (uint32_t c = threadIdx.x; c < nchunk; c += THREADS) {
             uint16_t rb[8], ad[8];
             unpack8(reinterpret_cast<const uint4*>(a.res_in)[c], rb);
-            if (a.addend != nullptr) unpack8(reinterpret_cast<const uint4*>(a.addend)[c], ad);
+            if (a.addend != nullptr) {
+                if (tagged) ld_tagged8(reinterpret_cast<const uint32_t*>(a.addend) + 8u * c, in_tag, a.sh, ad);
+                else unpack8(reinterpret_cast<const uint4*>(a.addend)[c], ad);
+            }
             float rf[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -269,6 +277,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
 
     float best_v = -INFINITY;
     int32_t best_i = INT32_MAX;
+    // where the outputs go: y, or (sharded) slot `rank` of every rank's gathered vector as tagged
+    // words, one destination rank per lane; logits of a sharded lm_head stay local
+    const bool push = (EPI != EPI_ARGMAX) && a.sh.out_slot != 0u;
+    const uint32_t ndst = push ? a.sh.world : 1u;
+    uint32_t* wdst = reinterpret_cast<uint32_t*>(a.sh.out_peer[lane & 7u]) + (size_t)a.sh.rank * a.sh.out_slot;
+    const uint32_t out_tag = push ? shard_tag(a.sh, a.sh.out_seq_mul, a.sh.out_seq_add) << 16 : 0u;
+    auto put_y = [&](uint32_t i, uint16_t yb) {
+        if (push) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(wdst + i), "r"(out_tag | (uint32_t)yb) : "memory");
+        else a.y[i] = yb;
+    };
 
     // multiply-accumulate one batch held in `raw` (or in `wide` when it was converted early)
     auto mac_batch = [&](auto& raw, bool use_wide, uint32_t i0, float2 (&acc_a)[R], float2 (&acc_b)[R]) {
@@ -306,14 +324,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
             }
             tot[r] = s;
         }
-        if (lane == 0) {
+        if (lane < ndst) {      // the sums are the same in every lane
             if constexpr (EPI == EPI_SWIGLU) {
                 static_assert(EPI != EPI_SWIGLU || R == 2, "SwiGLU epilogue works on row pairs");
                 const uint32_t row = g * R;
                 if (row + 1 < a.N) {
                     const float gt = __uint_as_float((uint32_t)f32_to_bf16_bits(tot[0]) << 16);
                     const float up = __uint_as_float((uint32_t)f32_to_bf16_bits(tot[R - 1]) << 16);
-                    a.y[row >> 1] = f32_to_bf16_bits(swiglu_f32(gt, up));
+                    put_y(row >> 1, f32_to_bf16_bits(swiglu_f32(gt, up)));
                 }
             } else {
 #pragma unroll
@@ -321,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a)
                     const uint32_t row = g * R + r;
                     if (row < a.N) {
                         const uint16_t yb = f32_to_bf16_bits(tot[r]);
-                        a.y[row] = yb;
+                        put_y(row, yb);
                         if constexpr (EPI == EPI_ARGMAX) {
                             const float v = __uint_as_float((uint32_t)yb << 16);
                             const int32_t idx = (int32_t)row + a.index_base;

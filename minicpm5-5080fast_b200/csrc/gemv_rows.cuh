@@ -54,6 +54,8 @@ struct RowsArgs {
     float* stage_val;
     int32_t* stage_idx;
     int32_t index_base;
+    // N-sharded exchange with peer GPUs (gemv_fast_kernel only; all zero = off)
+    ShardIO sh;
 };
 
 // ---- per-unit multiply-accumulate -------------------------------------------------

@@ -685,18 +685,16 @@ mc_status_t mc_sm100_lm_head_argmax(const void* d_w, const float* d_scale, const
     return mc_sm100_argmax_bf16(d_logits, M, N, y_stride, index_base, d_stage, d_out_idx, d_out_val, stream, pdl);
 }
 
-mc_status_t mc_sm100_lm_head_argmax_prologue(const void* d_w, const float* d_scale, const uint16_t* d_res_in,
-                                             const uint16_t* d_addend, const uint16_t* d_norm_w,
-                                             uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n,
-                                             float eps, int32_t index_base, void* d_stage,
-                                             int32_t* d_out_idx, float* d_out_val, void* stream,
-                                             int32_t pdl) {
-    clear_error();
+static mc_status_t lm_head_prologue_impl(const char* who, const void* d_w, const float* d_scale, const uint16_t* d_res_in,
+                                         const uint16_t* d_addend, const uint16_t* d_norm_w, uint16_t* d_res_out,
+                                         uint16_t* d_logits, uint32_t N, uint32_t n, float eps, int32_t index_base,
+                                         void* d_stage, int32_t* d_out_idx, float* d_out_val,
+                                         const mc_sm100_shard_io_t* io, void* stream, int32_t pdl) {
     const int wb = d_scale == nullptr ? 2 : 1;
     if (d_w == nullptr || d_res_in == nullptr || d_norm_w == nullptr || d_res_out == nullptr ||
         d_logits == nullptr || d_stage == nullptr || d_out_idx == nullptr || N == 0 || n == 0 ||
         (n % (wb == 2 ? 8u : 16u)) != 0 || !aligned16(d_w) || d_res_in == d_res_out) {
-        set_error("mc_sm100_lm_head_argmax_prologue: invalid args (N=%u n=%u)", N, n);
+        set_error("%s: invalid args (N=%u n=%u)", who, N, n);
         return MC_E_INVALID_ARGUMENT;
     }
     const cudaStream_t st = (cudaStream_t)stream;
@@ -707,12 +705,43 @@ mc_status_t mc_sm100_lm_head_argmax_prologue(const void* d_w, const float* d_sca
     a.w = d_w; a.scale = d_scale; a.y = d_logits; a.N = N; a.K = n; a.y_stride = N; a.kseg = n;
     a.res_in = d_res_in; a.addend = d_addend; a.norm_w = d_norm_w; a.res_out = d_res_out; a.eps = eps;
     a.stage_val = sv; a.stage_idx = si; a.index_base = index_base;
-    const mc_status_t s = rows(wb, 1, PRO_RESNORM, EPI_ARGMAX, a, 1, st, pdl != 0);
+    mc_status_t s;
+    if (io != nullptr) {
+        // the addend is a tagged vector gathered from all ranks: only the decode-chain kernel reads those
+        s = shard_io_to_args(who, io, N, false, a.sh);
+        if (s != MC_OK) return s;
+        s = wb == 2 ? launch_fast<2>(PRO_RESNORM, EPI_ARGMAX, a, st, pdl != 0) : launch_fast<1>(PRO_RESNORM, EPI_ARGMAX, a, st, pdl != 0);
+    } else {
+        s = rows(wb, 1, PRO_RESNORM, EPI_ARGMAX, a, 1, st, pdl != 0);
+    }
     if (s != MC_OK) return s;
     (void)launch(argmax_stage2_kernel, dim3(1), dim3(256), 0, st, pdl != 0, (const float*)sv,
                  (const int32_t*)si, kArgmaxCands, 1u, 0, d_out_idx, d_out_val);
     MCL_CHECK_LAUNCH("argmax_stage2");
     return MC_OK;
+}
+
+mc_status_t mc_sm100_lm_head_argmax_prologue(const void* d_w, const float* d_scale, const uint16_t* d_res_in,
+                                             const uint16_t* d_addend, const uint16_t* d_norm_w,
+                                             uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n,
+                                             float eps, int32_t index_base, void* d_stage,
+                                             int32_t* d_out_idx, float* d_out_val, void* stream,
+                                             int32_t pdl) {
+    clear_error();
+    return lm_head_prologue_impl("mc_sm100_lm_head_argmax_prologue", d_w, d_scale, d_res_in, d_addend, d_norm_w, d_res_out,
+                                 d_logits, N, n, eps, index_base, d_stage, d_out_idx, d_out_val, nullptr, stream, pdl);
+}
+
+mc_status_t mc_sm100_lm_head_argmax_sharded(const void* d_w, const float* d_scale, const uint16_t* d_res_in,
+                                            const uint16_t* d_addend, const uint16_t* d_norm_w,
+                                            uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n,
+                                            float eps, int32_t index_base, void* d_stage, int32_t* d_out_idx,
+                                            float* d_out_val, const mc_sm100_shard_io_t* io, void* stream,
+                                            int32_t pdl) {
+    clear_error();
+    if (io == nullptr) { set_error("mc_sm100_lm_head_argmax_sharded: no exchange descriptor"); return MC_E_INVALID_ARGUMENT; }
+    return lm_head_prologue_impl("mc_sm100_lm_head_argmax_sharded", d_w, d_scale, d_res_in, d_addend, d_norm_w, d_res_out,
+                                 d_logits, N, n, eps, index_base, d_stage, d_out_idx, d_out_val, io, stream, pdl);
 }
 
 // ---- host-buffer convenience -----------------------------------------------------------

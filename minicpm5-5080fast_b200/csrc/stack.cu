@@ -32,6 +32,16 @@ struct Layout {
     size_t total;
 };
 
+// Rows [lo, lo + rows) of an n-row tensor owned by `rank`; pitch = ceil(n / world) rounded up to 8.
+struct Span { uint32_t lo, rows, pitch; };
+static Span shard_span(uint32_t n, uint32_t world, uint32_t rank) {
+    if (world <= 1u) return {0u, n, n};
+    const uint32_t pitch = ((n + world - 1u) / world + 7u) & ~7u;
+    const uint32_t lo = rank * pitch < n ? rank * pitch : n;
+    return {lo, (n - lo < pitch ? n - lo : pitch), pitch};
+}
+static uint32_t world_of(const mc_sm100_stack_desc_t* d) { return d->world <= 1u ? 1u : d->world; }
+
 static bool valid_desc(const mc_sm100_stack_desc_t* d) {
     if (d == nullptr || d->struct_size != sizeof(mc_sm100_stack_desc_t)) return false;
     if (d->layers == 0 || d->hidden == 0 || d->qkv_rows < d->hidden || d->inter == 0 || d->vocab == 0) return false;
@@ -39,18 +49,29 @@ static bool valid_desc(const mc_sm100_stack_desc_t* d) {
     if (d->max_batch == 0 || d->max_batch > 64u) return false;
     const uint32_t mult = d->precision == 2u ? 16u : 8u;
     if (d->hidden % mult != 0 || d->inter % mult != 0) return false;
-    for (int i = 0; i < 4; ++i)
-        if (d->reserved[i] != 0) return false;
+    if (d->reserved[0] != 0 || d->reserved[1] != 0) return false;
+    if (d->world > 8u || (d->world > 1u && d->rank >= d->world) || (d->world <= 1u && d->rank != 0)) return false;
+    if (d->world > 1u) {
+        // every rank owns at least one row of every layer linear; sharded steps are M = 1
+        const uint32_t w = d->world;
+        if (shard_span(d->qkv_rows, w, w - 1u).rows == 0 || shard_span(d->hidden, w, w - 1u).rows == 0 ||
+            shard_span(d->inter, w, w - 1u).rows == 0 || shard_span(d->vocab, w, w - 1u).rows == 0)
+            return false;
+    }
     return true;
 }
 
 static Layout make_layout(const mc_sm100_stack_desc_t* d) {
     Layout L{};
     const size_t wb = d->precision == 2u ? 1u : 2u;
-    const size_t H = d->hidden, Q = d->qkv_rows, I = d->inter, V = d->vocab;
+    const uint32_t W = world_of(d), R = d->rank;
+    const size_t H = d->hidden, I = d->inter;
+    // rows of this rank's shard (the whole tensor on one GPU)
+    const size_t Q = shard_span(d->qkv_rows, W, R).rows, Ho = shard_span(d->hidden, W, R).rows,
+                 Ip = shard_span(d->inter, W, R).rows, V = shard_span(d->vocab, W, R).rows;
     const bool fp8 = d->precision == 2u;
-    const size_t sizes[10] = {Q * H * wb, H * H * wb, 2 * I * H * wb, H * I * wb, H * 2, H * 2,
-                              fp8 ? Q * 4 : 0, fp8 ? H * 4 : 0, fp8 ? 2 * I * 4 : 0, fp8 ? H * 4 : 0};
+    const size_t sizes[10] = {Q * H * wb, Ho * H * wb, 2 * Ip * H * wb, Ho * I * wb, H * 2, H * 2,
+                              fp8 ? Q * 4 : 0, fp8 ? Ho * 4 : 0, fp8 ? 2 * Ip * 4 : 0, fp8 ? Ho * 4 : 0};
     size_t off = 0;
     for (int i = 0; i < 10; ++i) {
         L.per_layer[i] = sizes[i];
@@ -71,7 +92,7 @@ static Layout make_layout(const mc_sm100_stack_desc_t* d) {
 
 // activation scratch (bf16 unless noted), all 256-byte aligned
 struct Scratch {
-    size_t x, res_a, res_b, h, qkv, ctx, o, mid, down, logits, stage, tokens, vals, total;
+    size_t x, res_a, res_b, h, qkv, ctx, o, mid, down, logits, stage, tokens, vals, sync, total;
 };
 
 static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
@@ -83,8 +104,35 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
     s.qkv = take(M * d->qkv_rows * 2); s.ctx = take(M * H * 2); s.o = take(M * H * 2);
     s.mid = take(M * (size_t)d->inter * 2); s.down = take(M * H * 2); s.logits = take(M * (size_t)d->vocab * 2);
     s.stage = take(mc_sm100_argmax_stage_bytes(d->max_batch)); s.tokens = take(M * 4); s.vals = take(M * 4);
+    s.sync = take(256);   // sharded: [0] step counter, [1] failure word, [2] shard token, [16..] peer address tables
     s.total = off;
     return s;
+}
+
+// Exchange region of a sharded stack, identical on every rank: the four gathered vectors of
+// a layer (tagged 32-bit words), then the (value, index) pairs of the greedy reduction and
+// their arrival counters.
+enum : uint32_t { XK_QKV = 0, XK_O = 1, XK_MID = 2, XK_DOWN = 3, XK_VECS = 4 };
+struct Exchange {
+    size_t buf[XK_VECS];     // gathered qkv, o, mid, down
+    uint32_t pitch[XK_VECS]; // slot pitch in words
+    size_t pairs, pair_flags;   // 8 x 8 bytes, 8 x uint32
+    size_t bytes;
+};
+static Exchange make_exchange(const mc_sm100_stack_desc_t* d) {
+    Exchange x{};
+    const uint32_t W = world_of(d);
+    const uint32_t dims[XK_VECS] = {d->qkv_rows, d->hidden, d->inter, d->hidden};
+    size_t off = 0;
+    for (uint32_t k = 0; k < XK_VECS; ++k) {
+        x.pitch[k] = shard_span(dims[k], W, 0).pitch;
+        x.buf[k] = off;
+        off += align256((size_t)x.pitch[k] * W * 4u);
+    }
+    x.pairs = off; off += align256(8u * 8u);
+    x.pair_flags = off; off += align256(8u * 4u);
+    x.bytes = off;
+    return x;
 }
 
 }  // namespace mcl
@@ -92,6 +140,9 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
 using namespace mcl;
 
 struct mc_sm100_stack {
+    Exchange xch;
+    uint64_t peer[8];              // exchange regions of all ranks as mapped here (0 = not bound)
+    uint64_t timeout_ns;
     mc_sm100_stack_desc_t desc;
     Layout lay;
     Scratch scr;
@@ -104,6 +155,73 @@ struct mc_sm100_stack {
 static const void* sec(const mc_sm100_stack* st, uint32_t layer, uint32_t which) {
     if (which < 10) return st->lay.per_layer[which] ? st->w + st->lay.layer_bytes * layer + st->lay.layer_off[which] : nullptr;
     return st->lay.top_bytes[which - 10] ? st->w + st->lay.top_off[which - 10] : nullptr;
+}
+
+// Sharded M = 1 step: the fused chain with every output exchanged inside the GEMV kernels.
+// Exchange kind k happens once per layer; its sequence number in step s (from 1), layer l is
+// (s - 1) * layers + l + 1.  Every rank carries the whole residual stream redundantly.
+static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int32_t* d_tokens, cudaStream_t stream) {
+    const mc_sm100_stack_desc_t& d = st->desc;
+    const uint32_t W = d.world, R = d.rank, H = d.hidden, I = d.inter, L = d.layers;
+    if (st->peer[R] == 0) { set_error("stack step: sharded stack without a bound exchange region"); return MC_E_INVALID_ARGUMENT; }
+    const bool fp8 = d.precision == 2u;
+    const Exchange& x = st->xch;
+    const uint64_t own = st->peer[R];
+    const uint32_t rows_q = shard_span(d.qkv_rows, W, R).rows, rows_h = shard_span(H, W, R).rows,
+                   rows_i = shard_span(I, W, R).rows;
+    const Span sv = shard_span(d.vocab, W, R);
+    uint32_t* sync = reinterpret_cast<uint32_t*>(st->s + st->scr.sync);
+    auto buf = [&](size_t off) { return reinterpret_cast<uint16_t*>(st->s + off); };
+    uint16_t *ra = buf(st->scr.res_a), *rb = buf(st->scr.res_b), *logits = buf(st->scr.logits);
+    // gathered vectors are uint32 words; the sharded entry points take them through their bf16 pointer arguments
+    auto gathered = [&](uint32_t k) { return reinterpret_cast<const uint16_t*>(own + x.buf[k]); };
+    // consume: exchange kind read by this linear (-1: local input) and its number within the step;
+    // produce: kind written (-1: output stays local) and its number
+    auto io = [&](int consume, uint32_t in_add, int produce, uint32_t out_add) {
+        mc_sm100_shard_io_t o{};
+        o.struct_size = sizeof(o); o.world = W; o.rank = R;
+        o.d_step = sync; o.d_status = reinterpret_cast<int32_t*>(sync + 1); o.timeout_ns = st->timeout_ns;
+        if (consume >= 0) { o.in_tagged = 1; o.in_seq_mul = L; o.in_seq_add = in_add; }
+        if (produce >= 0) {
+            o.out_slot = x.pitch[produce]; o.out_seq_mul = L; o.out_seq_add = out_add;
+            for (uint32_t p = 0; p < W; ++p) o.out_peer[p] = st->peer[p] + x.buf[produce];
+        }
+        return o;
+    };
+    void* sp = (void*)stream;
+    mc_status_t rc = MC_OK;
+#define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
+    const uint16_t* res_in = d_x;
+    for (uint32_t l = 0; l < L; ++l) {
+        const uint16_t *n1 = (const uint16_t*)sec(st, l, SEC_NORM1), *n2 = (const uint16_t*)sec(st, l, SEC_NORM2);
+        const float* no_scale = nullptr;
+        auto scale = [&](uint32_t which) { return fp8 ? (const float*)sec(st, l, which) : no_scale; };
+        mc_sm100_shard_io_t q = io(l == 0 ? -1 : (int)XK_DOWN, l, XK_QKV, l + 1);
+        STEP(mc_sm100_gemv_sharded(1, 0, sec(st, l, SEC_QKV), scale(SEC_QKV_SCALE), res_in, l == 0 ? nullptr : gathered(XK_DOWN),
+                                   n1, rb, nullptr, rows_q, H, d.eps, &q, sp, 1));
+        q = io(XK_QKV, l + 1, XK_O, l + 1);
+        STEP(mc_sm100_gemv_sharded(0, 0, sec(st, l, SEC_O), scale(SEC_O_SCALE), gathered(XK_QKV), nullptr, nullptr, nullptr,
+                                   nullptr, rows_h, H, d.eps, &q, sp, 1));
+        q = io(XK_O, l + 1, XK_MID, l + 1);
+        STEP(mc_sm100_gemv_sharded(1, 1, sec(st, l, SEC_GATE_UP), scale(SEC_GATE_UP_SCALE), rb, gathered(XK_O), n2, ra, nullptr,
+                                   2u * rows_i, H, d.eps, &q, sp, 1));
+        q = io(XK_MID, l + 1, XK_DOWN, l + 1);
+        STEP(mc_sm100_gemv_sharded(0, 0, sec(st, l, SEC_DOWN), scale(SEC_DOWN_SCALE), gathered(XK_MID), nullptr, nullptr, nullptr,
+                                   nullptr, rows_h, I, d.eps, &q, sp, 1));
+        res_in = ra;
+    }
+    const mc_sm100_shard_io_t q = io(XK_DOWN, L, -1, 0);
+    float* shard_val = reinterpret_cast<float*>(sync + 3);
+    int32_t* shard_tok = reinterpret_cast<int32_t*>(sync + 2);
+    STEP(mc_sm100_lm_head_argmax_sharded(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), res_in,
+                                         gathered(XK_DOWN), (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), rb, logits, sv.rows, H,
+                                         d.eps, (int32_t)sv.lo, st->s + st->scr.stage, shard_tok, shard_val, &q, sp, 1));
+    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, reinterpret_cast<const uint64_t*>(sync + 16),
+                              reinterpret_cast<const uint64_t*>(sync + 32), reinterpret_cast<const uint64_t*>(own + x.pairs),
+                              reinterpret_cast<const uint32_t*>(own + x.pair_flags), sync, R, W, st->timeout_ns,
+                              reinterpret_cast<int32_t*>(sync + 1), d_tokens, reinterpret_cast<float*>(st->s + st->scr.vals), sp, 1));
+#undef STEP
+    return MC_OK;
 }
 
 // One step for M rows; every launch goes to `stream`, nothing synchronises.
@@ -119,6 +237,10 @@ static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M,
     float* vals = reinterpret_cast<float*>(st->s + st->scr.vals);
     void* sp = (void*)stream;
     mc_status_t rc = MC_OK;
+    if (d.world > 1u) {
+        if (M != 1) { set_error("stack step: a sharded stack serves M = 1 (got %u)", M); return MC_E_UNSUPPORTED; }
+        return run_step_sharded(st, d_x, d_tokens, stream);
+    }
 #define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
     if (M == 1) {
         // fused chain: residual add + RMSNorm live in the GEMV prologues, SwiGLU in the gate_up epilogue
@@ -212,9 +334,62 @@ mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_wei
     st->scr = make_scratch(desc);
     st->w = (uint8_t*)d_weights;
     st->s = (uint8_t*)d_scratch;
+    st->xch = make_exchange(desc);
+    std::memset(st->peer, 0, sizeof(st->peer));
+    st->timeout_ns = 0;
     std::memset(st->graph, 0, sizeof(st->graph));
     std::memset(st->graph_stream, 0, sizeof(st->graph_stream));
     *out = st;
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_stack_exchange_bytes(const mc_sm100_stack_desc_t* desc, uint64_t* bytes) {
+    clear_error();
+    if (!valid_desc(desc) || bytes == nullptr) { set_error("mc_sm100_stack_exchange_bytes: invalid descriptor"); return MC_E_INVALID_ARGUMENT; }
+    *bytes = desc->world > 1u ? make_exchange(desc).bytes : 0u;
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t st, const uint64_t* h_peer_addrs, uint64_t timeout_ns, void* stream) {
+    clear_error();
+    if (st == nullptr || h_peer_addrs == nullptr || st->desc.world <= 1u) {
+        set_error("mc_sm100_stack_bind_exchange: invalid args (not a sharded stack?)");
+        return MC_E_INVALID_ARGUMENT;
+    }
+    const uint32_t W = st->desc.world, R = st->desc.rank;
+    for (uint32_t p = 0; p < W; ++p)
+        if (h_peer_addrs[p] == 0 || (h_peer_addrs[p] & 255u) != 0) {
+            set_error("mc_sm100_stack_bind_exchange: address of rank %u missing or not 256-byte aligned", p);
+            return MC_E_INVALID_ARGUMENT;
+        }
+    // graphs captured against an earlier binding hold its addresses
+    for (auto& g : st->graph)
+        if (g != nullptr) { cudaGraphExecDestroy(g); g = nullptr; }
+    const cudaStream_t s = (cudaStream_t)stream;
+    uint32_t words[64] = {0};
+    words[0] = 1u;   // step counter starts at 1; [1] failure word = 0
+    uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);
+    for (uint32_t p = 0; p < W; ++p) {
+        st->peer[p] = h_peer_addrs[p];
+        tables[p] = h_peer_addrs[p] + st->xch.pairs;
+        tables[8 + p] = h_peer_addrs[p] + st->xch.pair_flags;
+    }
+    st->timeout_ns = timeout_ns;
+    cudaError_t e = cudaMemsetAsync(reinterpret_cast<void*>(st->peer[R]), 0, st->xch.bytes, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(st->s + st->scr.sync, words, sizeof(words), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { set_error("mc_sm100_stack_bind_exchange: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_stack_exchange_status(mc_sm100_stack_t st, int32_t* h_status, void* stream) {
+    clear_error();
+    if (st == nullptr || h_status == nullptr) { set_error("mc_sm100_stack_exchange_status: invalid args"); return MC_E_INVALID_ARGUMENT; }
+    if (st->desc.world <= 1u) { *h_status = 0; return MC_OK; }
+    const cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(h_status, st->s + st->scr.sync + 4, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { set_error("mc_sm100_stack_exchange_status: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
     return MC_OK;
 }
 
