@@ -10,9 +10,9 @@
 
 namespace mcl {
 
-template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int T>
+template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int T, int MINB = 1>
 inline mc_status_t launch_fast_one(const RowsArgs& a, cudaStream_t stream, bool pdl) {
-    auto kern = gemv_fast_kernel<WB, R, U, PRE, DB, PRO, EPI, T>;
+    auto kern = gemv_fast_kernel<WB, R, U, PRE, DB, PRO, EPI, T, MINB>;
     const size_t smem = (size_t)a.K * (WB == 1 ? 4u : 2u) + (PRO == PRO_RESNORM ? (size_t)a.K * 4u : 0u);
     static size_t smem_set = 48u * 1024u;
     if (smem > smem_set) {
@@ -36,24 +36,32 @@ inline mc_status_t launch_fast_one(const RowsArgs& a, cudaStream_t stream, bool 
     return MC_OK;
 }
 
-// Tile shapes, from a sweep on B200 (graph replay, PDL, rotating weight copies):
-//  * a second register buffer (DB) and early widening (PRE) both cost registers and were
-//    slower than the plain form on every shape tried, so neither is selected here;
-//  * e4m3: two rows per warp share each shared-memory read of x, which is what lifts the
-//    large-N case (lm_head 57 -> 45 us); bf16 is best with one row per warp.
+// Tile shapes, from sweeps on B200 over the whole 40-layer chain (graph replay, PDL, every
+// layer its own weights), one linear's shape varied at a time:
+//  * a second register buffer (DB) and early widening (PRE) cost registers and were slower on
+//    every shape, so neither is selected;
+//  * e4m3: two rows per warp share each shared-memory read of x (lm_head 57 -> 45 us);
+//  * the matrix that fits ONE round of a 512-thread CTA (o_proj) gains ~1 us per call from a
+//    register budget of two CTAs per SM: the next kernel's CTA is then resident beside it and
+//    streams its weights while this one computes.  Larger shapes lose more from the smaller
+//    register file share than they gain.
 template <int WB, int PRO, int EPI>
 inline mc_status_t launch_fast_rows(const RowsArgs& a, cudaStream_t stream, bool pdl) {
     const uint32_t per_lane = (a.K * WB / 16u + 31u) / 32u;
     const uint32_t sms = (uint32_t)sm_count();
     if constexpr (WB == 2) {
         if (per_lane <= 9) {
-            if (a.N <= 24u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 768>(a, stream, pdl);   // one round
+            if (a.N <= 16u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 512, 2>(a, stream, pdl);   // one round, co-resident
+            if (a.N <= 24u * sms) return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 768>(a, stream, pdl);     // one round
             return launch_fast_one<2, 1, 9, false, false, PRO, EPI, 1024>(a, stream, pdl);
         }
         if (per_lane <= 24 && a.N <= 16u * sms) return launch_fast_one<2, 1, 24, false, false, PRO, EPI, 512>(a, stream, pdl);
         return launch_fast_one<2, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
     } else {
-        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, false, PRO, EPI, 1024>(a, stream, pdl);
+        if (per_lane <= 5) {
+            if (a.N <= 32u * sms) return launch_fast_one<1, 2, 5, false, false, PRO, EPI, 512>(a, stream, pdl);     // one round of row pairs
+            return launch_fast_one<1, 2, 5, false, false, PRO, EPI, 1024>(a, stream, pdl);
+        }
         if (per_lane <= 12 && a.N <= 16u * sms) return launch_fast_one<1, 1, 12, false, false, PRO, EPI, 512>(a, stream, pdl);
         return launch_fast_one<1, 2, 6, false, false, PRO, EPI, 512>(a, stream, pdl);
     }
@@ -67,7 +75,7 @@ inline mc_status_t launch_fast_pairs(const RowsArgs& a, cudaStream_t stream, boo
         if (per_lane <= 9) return launch_fast_one<2, 2, 9, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
         return launch_fast_one<2, 2, 12, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
     } else {
-        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, false, PRO, EPI_SWIGLU, 1024>(a, stream, pdl);
+        if (per_lane <= 5) return launch_fast_one<1, 2, 5, false, false, PRO, EPI_SWIGLU, 768>(a, stream, pdl);
         return launch_fast_one<1, 2, 6, false, false, PRO, EPI_SWIGLU, 512>(a, stream, pdl);
     }
 }

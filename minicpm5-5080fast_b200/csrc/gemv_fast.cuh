@@ -148,8 +148,10 @@ __device__ __forceinline__ void unpack8(const uint4& q, uint16_t (&bits)[8]) {
 // hardware conversion of the first batch before griddepcontrol.wait (twice the registers).
 // DB: keep a second register buffer so that, when a warp walks several row groups, the
 // next group's loads are issued before the current group's arithmetic.
-template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int THREADS>
-__global__ void __launch_bounds__(THREADS, 1) gemv_fast_kernel(const RowsArgs a) {
+// MINB: CTAs per SM the register budget is sized for.  With 2, the CTA of the NEXT kernel in a
+// chain becomes resident beside this one and has its weights in flight while this one computes.
+template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int THREADS, int MINB = 1>
+__global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs a) {
     static_assert(EPI != EPI_PARTIAL, "split-K partials are produced by gemv_rows_kernel");
     static_assert(!(PRE && WB == 2), "bf16 weights are consumed as loaded");
     extern __shared__ __align__(16) uint8_t smem_raw[];
