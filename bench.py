@@ -652,7 +652,11 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_kind": f"{peak_kind} copy bandwidth", "frac_of_nominal_8TBs": per_gpu / NOMINAL_HBM_GBS,
                          "kernel": ("gemv_fast_kernel" if args.m == 1 else "skinny_gemm_kernel" if args.m > 4 else "gemv_rows_kernel")
-                         + " (whole step: every launch of the chain)", "traffic": None},
+                         + (" (one launch per call)" if single else " (whole step: every launch of the chain)"),
+                         # DRAM bytes per step from ncu captures of the same kernels (profiles/): read + write =
+                         # 1.0002 - 1.001 x the algorithmic bytes on every captured shape; scaled by the bytes processed
+                         "traffic": (total_bytes / world) * 1.0005 / (1 if not single else st.copies),
+                         "traffic_source": "ncu dram__bytes_read+write of gemv_fast_kernel / skinny_gemm_kernel captures, scaled"},
         }
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
