@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory from the reference's own
 Python implementation.
 
-Run in a container where the reference tree is mounted (default
-/root/reference, override with REF_ROOT):
+Run where the reference tree is available (by default a directory `reference`
+beside this repository; override with REF_ROOT):
 
     python tests/golden/make_golden.py
 
@@ -22,7 +22,7 @@ import types
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("REF_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("REF_ROOT", os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference")))
 sys.path.insert(0, os.path.join(REF_ROOT, "tools"))
 sys.path.insert(0, os.path.join(HERE, "..", "..", "oracle"))
 
