@@ -454,6 +454,28 @@ MC_SM100_API mc_status_t mc_sm100_wpk_upload(mc_sm100_wpk_t wpk, const char* nam
                                              uint32_t row_hi, int32_t interleave, void* d_data,
                                              uint64_t data_capacity, float* d_scale, void* stream);
 
+/* Writer of the same container and the packer's e4m3 quantiser, on the host (role of the writer in
+ * tools/minicpm_common.py:318-348 and of tools/quantize.py:85-113).  Files it writes are loadable by
+ * the reference (target_sm 120) and by mc_sm100_wpk_open.  max_sections reserves the table of
+ * contents: data starts at align256(64 + 132 * max_sections); sections are streamed to the file as
+ * they are added (data 256-byte aligned, e4m3 sections carry their fp32 row scales directly behind
+ * the codes), finish writes header and table and closes the file. */
+typedef struct mc_sm100_wpk_writer* mc_sm100_wpk_writer_t;
+MC_SM100_API mc_status_t mc_sm100_wpk_writer_create(const char* path, uint32_t max_sections, uint32_t target_sm,
+                                                    const uint8_t* model_hash32, mc_sm100_wpk_writer_t* out);
+/* dtype 0: h_data = bf16 bits, h_scales NULL; dtype 2: h_data = e4m3 codes, h_scales = fp32 [dims[0]]. */
+MC_SM100_API mc_status_t mc_sm100_wpk_writer_add(mc_sm100_wpk_writer_t writer, const char* name, uint32_t dtype,
+                                                 uint32_t rank, const uint32_t* dims, const void* h_data,
+                                                 const float* h_scales);
+MC_SM100_API mc_status_t mc_sm100_wpk_writer_finish(mc_sm100_wpk_writer_t writer);   /* also frees the writer */
+MC_SM100_API void mc_sm100_wpk_writer_abort(mc_sm100_wpk_writer_t writer);           /* closes, deletes the file */
+/* bf16 weight [N,K] -> e4m3 codes + fp32 row scales with the packer's rule: scale = max|row| / 448
+ * floored at 1e-12, q = e4m3_rne_saturating(w / scale) (tools/minicpm_common.py:130-171, 204-212). */
+MC_SM100_API mc_status_t mc_sm100_quantize_rows_host(const uint16_t* h_w, uint32_t N, uint32_t K, uint8_t* h_q,
+                                                     float* h_scale);
+/* The encoder alone: n floats -> n e4m3 codes (round to nearest even, saturating, never 0x7F / 0xFF). */
+MC_SM100_API mc_status_t mc_sm100_e4m3_from_f32_host(const float* h_in, uint64_t n, uint8_t* h_out);
+
 /* ---------------------------------------------------------------- debug hook -- */
 
 /* Not part of the frozen surface (same standing as the reference's

@@ -79,6 +79,12 @@ SIGNATURES = {
     "mc_sm100_wpk_section_count": (_u32, [_vp]),
     "mc_sm100_wpk_find": (_i32, [_vp, C.c_char_p, _vp]),
     "mc_sm100_wpk_upload": (_i32, [_vp, C.c_char_p, _u32, _u32, _i32, _vp, C.c_uint64, _vp, _vp]),
+    "mc_sm100_wpk_writer_create": (_i32, [C.c_char_p, _u32, _u32, _vp, C.POINTER(_vp)]),
+    "mc_sm100_wpk_writer_add": (_i32, [_vp, C.c_char_p, _u32, _u32, _vp, _vp, _vp]),
+    "mc_sm100_wpk_writer_finish": (_i32, [_vp]),
+    "mc_sm100_wpk_writer_abort": (None, [_vp]),
+    "mc_sm100_quantize_rows_host": (_i32, [_vp, _u32, _u32, _vp, _vp]),
+    "mc_sm100_e4m3_from_f32_host": (_i32, [_vp, C.c_uint64, _vp]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -392,6 +398,42 @@ def wpk_find(h, name: str) -> WpkSection:
     sec = WpkSection()
     _check(lib().mc_sm100_wpk_find(h, name.encode(), C.byref(sec)))
     return sec
+
+
+def wpk_write(path: str, sections, target_sm: int = 120) -> None:
+    """sections: list of (name, bf16 uint16 array) or (name, e4m3 uint8 array, fp32 row scales); numpy arrays."""
+    import numpy as np
+    w = _vp()
+    _check(lib().mc_sm100_wpk_writer_create(path.encode(), len(sections), target_sm, None, C.byref(w)))
+    try:
+        for sec in sections:
+            name, arr = sec[0], np.ascontiguousarray(sec[1])
+            dims = (C.c_uint32 * arr.ndim)(*arr.shape)
+            sc = np.ascontiguousarray(sec[2], dtype=np.float32) if len(sec) == 3 else None
+            _check(lib().mc_sm100_wpk_writer_add(w, name.encode(), 2 if sc is not None else 0, arr.ndim, C.cast(dims, _vp),
+                                                 arr.ctypes.data, sc.ctypes.data if sc is not None else None))
+    except Exception:
+        lib().mc_sm100_wpk_writer_abort(w)
+        raise
+    _check(lib().mc_sm100_wpk_writer_finish(w))
+
+
+def quantize_rows_host(w_u16):
+    """bf16 weight [N, K] (numpy uint16) -> (e4m3 codes uint8 [N, K], fp32 row scales [N]) on the host."""
+    import numpy as np
+    w = np.ascontiguousarray(w_u16, dtype=np.uint16)
+    q = np.empty(w.shape, dtype=np.uint8)
+    sc = np.empty(w.shape[0], dtype=np.float32)
+    _check(lib().mc_sm100_quantize_rows_host(w.ctypes.data, w.shape[0], w.shape[1], q.ctypes.data, sc.ctypes.data))
+    return q, sc
+
+
+def e4m3_from_f32_host(values):
+    import numpy as np
+    v = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.empty(v.shape, dtype=np.uint8)
+    _check(lib().mc_sm100_e4m3_from_f32_host(v.ctypes.data, v.size, out.ctypes.data))
+    return out
 
 
 def wpk_upload(h, name, row_lo, row_hi, interleave, dst, scale_dst=None, stream=None):

@@ -11,9 +11,11 @@
 // payload is plain row-major and only the placement in device memory differs here.
 // What is new: a section can be uploaded as an N-shard (a row range) and the fused
 // gate_up section can be re-laid with gate and up rows interleaved on the way.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <string>
 #include <vector>
 
 #include "common.cuh"
@@ -42,9 +44,58 @@ static uint64_t fnv1a64(const char* s) {
     return h;
 }
 
+
+// ---- host-side quantiser of the packer -----------------------------------------------
+// float -> e4m3 code with the packer's rule (tools/minicpm_common.py:130-171): round to nearest
+// even on the 3-bit mantissa, magnitudes beyond 448 -- infinities and NaN included -- saturate
+// to +/-448, the codes 0x7F / 0xFF are never produced.  Done in exact double arithmetic: the
+// magnitude is put on the integer grid of its binade (2^(e-3), subnormal grid 2^-9) and rounded
+// half to even there.
+static uint8_t e4m3_from_f32(float f) {
+    uint32_t bits;
+    std::memcpy(&bits, &f, 4);
+    const uint8_t sign = (uint8_t)((bits >> 31) << 7);
+    double mag = std::fabs((double)f);
+    if (!std::isfinite(mag)) mag = 1e9;
+    int e = 0;
+    (void)std::frexp(mag, &e);
+    e -= 1;
+    if (e < -6 || mag == 0.0) e = -6;
+    const double step = std::ldexp(1.0, e - 3);
+    double val = std::nearbyint(mag / step) * step;          // default rounding mode: half to even
+    if (val > 448.0) val = 448.0;
+    uint32_t code;
+    if (val >= std::ldexp(1.0, -6)) {
+        int e2 = 0;
+        (void)std::frexp(val, &e2);
+        e2 -= 1;
+        code = ((uint32_t)(e2 + 7) << 3) + (uint32_t)(val / std::ldexp(1.0, e2) * 8.0 - 8.0);
+    } else {
+        code = (uint32_t)(val * 512.0);
+    }
+    if (code > 0x7Eu) code = 0x7Eu;
+    return (uint8_t)(sign | code);
+}
+
+static float bf16_bits_to_f32(uint16_t b) {
+    const uint32_t u = (uint32_t)b << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+
 }  // namespace mcl
 
 using namespace mcl;
+
+struct mc_sm100_wpk_writer {
+    FILE* f;
+    std::string path;
+    WpkHeader hdr;
+    std::vector<WpkToc> toc;
+    uint32_t max_sections;
+    uint64_t cursor;            // next free 256-byte aligned file offset
+};
 
 struct mc_sm100_wpk {
     FILE* f;
@@ -206,6 +257,125 @@ mc_status_t mc_sm100_wpk_upload(mc_sm100_wpk_t h, const char* name, uint32_t row
     mc_status_t rc = push(t->data_offset, row_bytes, (uint8_t*)d_data);
     if (rc == MC_OK && t->dtype == 2) rc = push(t->scale_offset, 4, (uint8_t*)d_scale);
     return rc;
+}
+
+// ---- writer + quantiser (role of tools/quantize.py and the writer of tools/minicpm_common.py) ----
+
+mc_status_t mc_sm100_quantize_rows_host(const uint16_t* h_w, uint32_t N, uint32_t K, uint8_t* h_q, float* h_scale) {
+    clear_error();
+    if (h_w == nullptr || h_q == nullptr || h_scale == nullptr || N == 0 || K == 0) {
+        set_error("mc_sm100_quantize_rows_host: invalid args (N=%u K=%u)", N, K);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    for (uint32_t n = 0; n < N; ++n) {
+        const uint16_t* row = h_w + (size_t)n * K;
+        float amax = 0.f;
+        for (uint32_t k = 0; k < K; ++k) {
+            const float a = std::fabs(bf16_bits_to_f32(row[k]));
+            if (a > amax || a != a) amax = a != a ? amax : a;
+        }
+        float sc = amax / 448.0f;                       // fp32 division, floored (minicpm_common.py:204-207)
+        if (!(sc > 1e-12f)) sc = 1e-12f;
+        h_scale[n] = sc;
+        for (uint32_t k = 0; k < K; ++k) h_q[(size_t)n * K + k] = e4m3_from_f32(bf16_bits_to_f32(row[k]) / sc);
+    }
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_e4m3_from_f32_host(const float* h_in, uint64_t n, uint8_t* h_out) {
+    clear_error();
+    if ((h_in == nullptr || h_out == nullptr) && n != 0) { set_error("mc_sm100_e4m3_from_f32_host: invalid args"); return MC_E_INVALID_ARGUMENT; }
+    for (uint64_t i = 0; i < n; ++i) h_out[i] = e4m3_from_f32(h_in[i]);
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_wpk_writer_create(const char* path, uint32_t max_sections, uint32_t target_sm, const uint8_t* model_hash32,
+                                       mc_sm100_wpk_writer_t* out) {
+    clear_error();
+    if (out != nullptr) *out = nullptr;
+    if (path == nullptr || out == nullptr || max_sections == 0 || (target_sm != 100u && target_sm != 120u)) {
+        set_error("mc_sm100_wpk_writer_create: invalid args (max_sections=%u target_sm=%u)", max_sections, target_sm);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    FILE* f = std::fopen(path, "wb");
+    if (f == nullptr) { set_error("wpk: cannot create '%s'", path); return MC_E_IO; }
+    mc_sm100_wpk_writer* w = new (std::nothrow) mc_sm100_wpk_writer();
+    if (w == nullptr) { std::fclose(f); set_error("wpk: out of host memory"); return MC_E_OUT_OF_MEMORY; }
+    w->f = f;
+    w->path = path;
+    std::memset(&w->hdr, 0, sizeof(w->hdr));
+    w->hdr.magic = 0x31504B4Du;
+    w->hdr.abi_version = 2;
+    w->hdr.target_sm = (uint16_t)target_sm;
+    if (model_hash32 != nullptr) std::memcpy(w->hdr.model_hash, model_hash32, 32);
+    w->hdr.toc_offset = 64;
+    w->hdr.data_start = (64u + (uint64_t)max_sections * sizeof(WpkToc) + 255u) & ~(uint64_t)255u;
+    w->max_sections = max_sections;
+    w->cursor = w->hdr.data_start;
+    *out = w;
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_wpk_writer_add(mc_sm100_wpk_writer_t w, const char* name, uint32_t dtype, uint32_t rank, const uint32_t* dims,
+                                    const void* h_data, const float* h_scales) {
+    clear_error();
+    if (w == nullptr || name == nullptr || dims == nullptr || h_data == nullptr || rank == 0 || rank > 8 || (dtype != 0 && dtype != 2) ||
+        (dtype == 2) != (h_scales != nullptr)) {
+        set_error("mc_sm100_wpk_writer_add: invalid args (dtype=%u rank=%u)", dtype, rank);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    if (w->toc.size() >= w->max_sections) { set_error("wpk writer: more than the %u sections announced", w->max_sections); return MC_E_INVALID_ARGUMENT; }
+    WpkToc t;
+    std::memset(&t, 0, sizeof(t));
+    t.name_hash = fnv1a64(name);
+    for (const auto& o : w->toc)
+        if (o.name_hash == t.name_hash) { set_error("wpk writer: section '%s' twice", name); return MC_E_INVALID_ARGUMENT; }
+    t.dtype = dtype; t.layout = 0; t.rank = rank;
+    uint64_t elems = 1;
+    for (uint32_t r = 0; r < rank; ++r) { t.dims[r] = dims[r]; elems *= dims[r]; }
+    t.data_offset = w->cursor;
+    t.data_bytes = elems * (dtype == 0 ? 2u : 1u);
+    bool ok = std::fseek(w->f, (long)t.data_offset, SEEK_SET) == 0 && (t.data_bytes == 0 || std::fwrite(h_data, 1, t.data_bytes, w->f) == t.data_bytes);
+    uint64_t end = t.data_offset + t.data_bytes;
+    if (dtype == 2) {                 // fp32 row scales directly behind the codes (tools/quantize.py:85-113)
+        t.scale_offset = end;
+        t.scale_bytes = (uint64_t)dims[0] * 4u;
+        ok = ok && std::fwrite(h_scales, 1, t.scale_bytes, w->f) == t.scale_bytes;
+        end += t.scale_bytes;
+    }
+    if (!ok) { set_error("wpk writer: write of section '%s' failed", name); return MC_E_IO; }
+    w->cursor = (end + 255u) & ~(uint64_t)255u;
+    w->toc.push_back(t);
+    return MC_OK;
+}
+
+mc_status_t mc_sm100_wpk_writer_finish(mc_sm100_wpk_writer_t w) {
+    clear_error();
+    if (w == nullptr) { set_error("mc_sm100_wpk_writer_finish: invalid args"); return MC_E_INVALID_ARGUMENT; }
+    w->hdr.section_count = (uint32_t)w->toc.size();
+    bool ok = std::fseek(w->f, 0, SEEK_SET) == 0 && std::fwrite(&w->hdr, sizeof(WpkHeader), 1, w->f) == 1 &&
+              (w->toc.empty() || std::fwrite(w->toc.data(), sizeof(WpkToc), w->toc.size(), w->f) == w->toc.size());
+    // pad the file to the aligned end, as the packer does
+    if (ok && w->cursor > 0) {
+        ok = std::fseek(w->f, 0, SEEK_END) == 0;
+        const uint64_t have = ok ? (uint64_t)std::ftell(w->f) : 0;
+        if (ok && have < w->cursor) {
+            const std::vector<uint8_t> zeros((size_t)(w->cursor - have), 0);
+            ok = std::fwrite(zeros.data(), 1, zeros.size(), w->f) == zeros.size();
+        }
+    }
+    ok = (std::fclose(w->f) == 0) && ok;
+    const std::string path = w->path;
+    delete w;
+    if (!ok) { set_error("wpk writer: finishing '%s' failed", path.c_str()); return MC_E_IO; }
+    return MC_OK;
+}
+
+void mc_sm100_wpk_writer_abort(mc_sm100_wpk_writer_t w) {
+    if (w == nullptr) return;
+    std::fclose(w->f);
+    std::remove(w->path.c_str());
+    delete w;
 }
 
 }  // extern "C"

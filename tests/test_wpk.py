@@ -99,3 +99,56 @@ def test_upload_shards_and_interleave(pkg, tmp_path):
             pkg.wpk_upload(h, "layer0.qkv", 0, 24, False, small)               # destination too small
     finally:
         pkg.wpk_close(h)
+
+
+def test_writer_is_byte_identical_to_the_packer_layout(pkg, tmp_path):
+    """The C writer against the restated packer (oracle/wpk_np.py): same bytes, and readable back."""
+    w, gu, q, sc, secs = _sections()
+    a, b = str(tmp_path / "oracle.wpk"), str(tmp_path / "lib.wpk")
+    wpk_np.write_wpk(a, secs)
+    pkg.wpk_write(b, secs)
+    assert open(a, "rb").read() == open(b, "rb").read()
+    h = pkg.wpk_open(b)
+    try:
+        s = pkg.wpk_find(h, "layer0.gate_up")
+        assert (s.dtype, s.dims[0], s.scale_bytes, s.scale_offset) == (2, 32, 32 * 4, s.data_offset + s.data_bytes)
+    finally:
+        pkg.wpk_close(h)
+    with pytest.raises(pkg.McError):                        # a section name twice
+        pkg.wpk_write(str(tmp_path / "dup.wpk"), [("a", w), ("a", w)])
+    assert not os.path.exists(str(tmp_path / "dup.wpk"))    # aborted writers leave no file behind
+
+
+def test_host_quantiser_matches_reference_fixture(pkg, golden):
+    """mc_sm100_quantize_rows_host against the reference packer's outputs (golden fixture) and the oracle."""
+    g = golden["codec"]
+    assert np.array_equal(pkg.e4m3_from_f32_host(g["enc_in"]), g["enc_out"])        # all 20999 reference encoder outputs
+    # through the row quantiser: every fixture input that is exact in bf16 and within +-448
+    # goes into a row whose maximum is 448, so that the row scale is exactly 1 and q = e4m3(v)
+    v = g["enc_in"]
+    exact = (onp.bf16_to_f32(onp.f32_to_bf16(v)) == v) & (np.abs(v) <= 448.0)
+    vin, want = v[exact], g["enc_out"][exact]
+    assert vin.size > 200           # code points, midpoints and boundaries of the fixture survive the bf16 filter
+    row = np.concatenate(([np.float32(448.0)], vin)).astype(np.float32)
+    pad = (-row.size) % 16
+    row = np.concatenate((row, np.zeros(pad, dtype=np.float32)))
+    q, sc = pkg.quantize_rows_host(onp.f32_to_bf16(row).reshape(1, -1))
+    assert sc[0] == np.float32(1.0) and np.array_equal(q[0, 1:1 + vin.size], want)
+    # the packer's row fixture (fp32 rows): rows that are exact in bf16 must reproduce codes and scales
+    rw = g["rows_w"]
+    rows_exact = np.all(onp.bf16_to_f32(onp.f32_to_bf16(rw)) == rw, axis=1)
+    if rows_exact.any():
+        q, sc = pkg.quantize_rows_host(onp.f32_to_bf16(rw[rows_exact]))
+        assert np.array_equal(q, g["rows_q"][rows_exact]) and np.array_equal(sc.view(np.uint32), g["rows_scale"][rows_exact].view(np.uint32))
+    rng = np.random.default_rng(77)
+    w = onp.f32_to_bf16((rng.standard_normal((64, 256)) * 0.02).astype(np.float32))
+    w[3, :] = 0                                             # all-zero row: scale floor 1e-12, codes 0
+    w[5, 7] = 0x7F80                                        # +inf saturates to 448
+    w[6, 9] = 0x7FC0                                        # NaN saturates too, never 0x7F
+    q, sc = pkg.quantize_rows_host(w)
+    with np.errstate(invalid="ignore", over="ignore", divide="ignore"):
+        rq, rsc = onp.make_fp8_weight(w)
+    rows = [r for r in range(64) if r not in (5, 6)]        # rows with inf/NaN: the row maximum itself is not finite
+    assert np.array_equal(q[rows], rq[rows]) and np.array_equal(sc[rows].view(np.uint32), rsc[rows].view(np.uint32))
+    assert sc[3] == np.float32(1e-12) and not q[3].any()
+    assert not np.any((q & 0x7F) == 0x7F)
