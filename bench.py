@@ -213,7 +213,8 @@ def workload_name(args):
     if getattr(args, "workload", "stream") != "stream":
         n, k, kind = Single.SHAPES[args.workload]
         extra = {0: "", 1: " + SwiGLU epilogue", 2: " + fused argmax"}[kind]
-        return f"single linear {args.workload} {k}->{n}{extra}, {args.dtype}, M={args.m}, rotating weight copies"
+        w8 = ", W8A8 (activations quantised per row)" if args.dtype == "fp8" and args.m > 1 and os.environ.get("MC_W8A8", "0") == "1" else ""
+        return f"single linear {args.workload} {k}->{n}{extra}, {args.dtype}{w8}, M={args.m}, rotating weight copies"
     return (f"config5 full 40-layer decode weight stream (qkv 2304->3456, o 2304->2304, gate_up 2304->11520 + SwiGLU, "
             f"down 5760->2304, lm_head 2304->122753 + argmax), {args.dtype}, M={args.m}")
 
@@ -507,6 +508,9 @@ class Single:
         self.ws_bytes = pkg.gemm_workspace_bytes(m, n, k)
         self.ws = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device="cuda")
         self.launches = 0
+        self.w8a8 = os.environ.get("MC_W8A8", "0") == "1"      # e4m3, M > 1: quantised activations instead of weight-only
+        self.xq = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+        self.xs = torch.empty(m, dtype=torch.float32, device="cuda")
         self.bytes_per_call = linear_bytes(n, k, m, wb, n_out)
 
     def step(self, pdl=True):
@@ -516,13 +520,16 @@ class Single:
                 p.launch_gate_up_swiglu(w, s, self.x, self.y, m, n, k, pdl=pdl)
             elif self.kind == 2 and m <= 8:
                 p.launch_lm_head_argmax(w, s, self.x, self.y, n, m, n, k, 0, self.stage, self.tok, None, pdl=pdl)
+            elif self.fp8 and self.w8a8 and m > 1:
+                # the reference's batched e4m3 path: per-row activation quantiser + W8A8 GEMM (tcgen05 kind::f8f6f4)
+                p.gemm_fp8(None, self.ws, self.ws_bytes, m, n, k, w, s, self.x, self.y, self.xq, self.xs)
             elif self.fp8:
                 (p.launch_gemv_fp8(w, s, self.x, self.y, n, k, pdl=pdl) if m == 1
                  else p.launch_gemv_fp8_rows_m(w, s, self.x, self.y, m, n, k, pdl=pdl))
             else:
                 (p.launch_decode_gemv(w, self.x, self.y, n, k, pdl=pdl) if m == 1
                  else p.gemm_bf16(None, self.ws, self.ws_bytes, m, n, k, w, self.x, self.y))
-        self.launches = self.copies * (2 if self.kind == 2 else 1)
+        self.launches = self.copies * (2 if self.kind == 2 or (self.fp8 and self.w8a8 and m > 1) else 1)
         return self.tok
 
 

@@ -190,6 +190,26 @@ def test_gate_up_swiglu_epilogue(pkg, g, golden, fp8, M, I, K):
         check_close(g.host_u16(dy), golden["baseline"][key], abs_floor=4e-3, what="config2 vs reference output")
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("M,I,K", [(5, 96, 256), (8, I_B, K_B), (16, 1000, 2048), (64, I_B, K_B)])
+def test_gate_up_swiglu_epilogue_batched(pkg, g, fp8, M, I, K):
+    """More than four rows: the tensor-core kernel with the SwiGLU in its epilogue.  The fused output is held to
+    2 bf16 ulp + floor and relL2 like every other result; the element-wise relative bound is 2e-2 here because a
+    one-ulp difference of gate or up (0.4 - 0.8 % each, a different accumulation order) goes straight into the product."""
+    w = onp.seeded_bf16(95 + I, (2 * I, K), 0.02)
+    x = onp.seeded_bf16(96 + I, (M, K), 1.0)
+    dy = g.empty_u16(M, I)
+    if fp8:
+        q, sc = onp.make_fp8_weight(w)
+        pkg.launch_gate_up_swiglu(interleaved(g, pkg, q, I), interleaved(g, pkg, sc.reshape(-1, 1), I), g.dev(x), dy, M, 2 * I, K)
+        ref = onp.gate_up_swiglu_fp8(q, sc, x)
+    else:
+        pkg.launch_gate_up_swiglu(interleaved(g, pkg, w, I), None, g.dev(x), dy, M, 2 * I, K)
+        ref = onp.gate_up_swiglu_bf16(w, x)
+    g.sync()
+    check_close(g.host_u16(dy), ref, abs_floor=4e-3, what=f"gate_up epilogue batched fp8={fp8} M={M} I={I}", rel_max=2e-2)
+
+
 # ---- batched -------------------------------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 16, 32, 64])
 @pytest.mark.parametrize("N,K", [(K_B, I_B), (2048, 6144), (264, 512)])
