@@ -239,7 +239,7 @@ class Stream:
         # kernels; "peer" = per-call launches + the library's peer all-gather kernel; "nccl" = per-call
         # launches + ncclAllGather.  The last two are kept as comparison arms.
         self.gather_mode = os.environ.get("MC_GATHER", "fused") if world > 1 else None
-        if world == 1 or (m == 1 and self.gather_mode == "fused"):
+        if world == 1 or self.gather_mode == "fused":
             # the weights live in the library's own arena layout (this rank's shard of it) and the
             # step is the library's decode-stack object (C ABI)
             self.desc = pkg.stack_desc(L, H, QKV, I, V, fp8=self.fp8, max_batch=max(m, 1), graph=True,
@@ -328,8 +328,8 @@ class Stream:
                 self.peer = None
                 self.peer_error = f"{type(e).__name__}: {e}"[:120]
         if m != 1:
-            if world != 1:
-                raise SystemExit("bench: the batched (M > 1) stream runs on one GPU")
+            if world != 1 and self.handle is None:
+                raise SystemExit("bench: the batched (M > 1) sharded stream runs through the library's stack (MC_GATHER=fused)")
             if m > 64:
                 raise SystemExit("bench: M <= 64")
             self.h = z(m, H)
@@ -423,7 +423,8 @@ class Stream:
         """One GPU: the whole step through the C ABI's decode-stack object."""
         m = self.m
         self.pkg.stack_step(self.handle, self.x_in, m, self.tok)
-        self.launches = (4 * L + 2 + (1 if self.world > 1 else 0)) if m == 1 else (6 * L + 1 + (2 if m <= 4 else 3))
+        self.launches = ((4 * L + 2 + (1 if self.world > 1 else 0)) if m == 1
+                         else (6 * L + 1 + (2 if m <= 4 else 3) + ((4 * L + 1) if self.world > 1 else 0)))
         return self.tok
 
     def step(self, pdl=True):
@@ -687,7 +688,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="stream", choices=["stream", "qkv", "o", "gate_up", "down", "lm_head"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"])
-    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--m", "--batch", dest="m", type=int, default=1, help="batch rows M (use --batch under torchrun, which claims --m)")
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline leg")
     args = ap.parse_args()

@@ -339,12 +339,13 @@ MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const 
 
 /* --------------------------------------------------------------- multi-GPU --- */
 
-/* Sharded stack (desc.world > 1, M = 1 only).  layers/hidden/qkv_rows/inter/vocab describe the WHOLE
+/* Sharded stack (desc.world > 1).  layers/hidden/qkv_rows/inter/vocab describe the WHOLE
  * model; every linear is split along its output rows (gate_up by (gate, up) pairs, lm_head by
  * vocab) with a uniform pitch of ceil(rows / world) rounded up to 8, rank r owning rows
  * [r*pitch, min(rows, (r+1)*pitch)); mc_sm100_stack_sizes / _section then describe THIS rank's
- * arena (norm weights whole).  Outputs travel between ranks inside the GEMV kernels
- * (mc_sm100_gemv_sharded) as tagged words, through an exchange region that every rank allocates in peer-mappable
+ * arena (norm weights whole).  At M = 1 outputs travel between ranks inside the GEMV kernels
+ * (mc_sm100_gemv_sharded) as tagged words; at M > 1 one small kernel per linear scatters the [M, rows]
+ * result into every rank's [M, width] buffer (mc_sm100_peer_allgather_rows).  Both go through an exchange region that every rank allocates in peer-mappable
  * memory (same size everywhere) and whose addresses, as mapped in this process, are bound once:
  *   mc_sm100_stack_exchange_bytes(desc, &n); allocate + map n bytes on every rank;
  *   mc_sm100_stack_bind_exchange(stack, addrs (host array [world], [rank] = own), stream);
@@ -371,6 +372,15 @@ MC_SM100_API mc_status_t mc_sm100_peer_allgather(const void* d_shard, uint32_t s
                                                  uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank,
                                                  uint32_t world, uint64_t timeout_ns, int32_t* d_status,
                                                  void* stream, int32_t pdl);
+/* The same for a batch: `rows` rows of row_bytes (contiguous in d_shard) land in column slot `rank` of
+ * every rank's row-major buffer: row m at byte m * dst_pitch_bytes + rank * slot_bytes (batched sharded
+ * linears: the gathered buffer is the [M, N] activation of the next GEMM). */
+MC_SM100_API mc_status_t mc_sm100_peer_allgather_rows(const void* d_shard, uint32_t rows, uint32_t row_bytes,
+                                                      uint32_t dst_pitch_bytes, uint32_t slot_bytes,
+                                                      const uint64_t* d_peer_bufs, const uint64_t* d_peer_flags,
+                                                      uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank,
+                                                      uint32_t world, uint64_t timeout_ns, int32_t* d_status,
+                                                      void* stream, int32_t pdl);
 
 /* Sharded M = 1 linear with the output exchange INSIDE the GEMV kernel (no counterpart in
  * the reference, which is single-GPU).  A gathered vector is an array of uint32 words, one per
@@ -414,12 +424,12 @@ MC_SM100_API mc_status_t mc_sm100_lm_head_argmax_sharded(
     int32_t index_base, void* d_stage, int32_t* d_out_idx, float* d_out_val, const mc_sm100_shard_io_t* io,
     void* stream, int32_t pdl);
 
-/* Greedy token over vocab shards in one single-CTA kernel: pushes this rank's (value, index)
- * to every rank (d_pair_peers: device array of `world` addresses of each rank's [world] x 8-byte
- * pair slots), signals, waits (bounded) for all ranks' pairs of step *d_step, reduces with the
- * reference's tie rule (lowest index, native/kernels/sm120/sampling.cu:26, 80), writes the token
- * and the value, and finally advances *d_step. */
-MC_SM100_API mc_status_t mc_sm100_peer_argmax(const float* d_val, const int32_t* d_idx,
+/* Greedy tokens over vocab shards in one single-CTA kernel: pushes this rank's (value, index) of each
+ * of n_rows rows to every rank (d_pair_peers: device array of `world` addresses of each rank's
+ * [world][n_rows] x 8-byte pair slots), signals, waits (bounded) for all ranks' pairs of step *d_step,
+ * reduces every row with the reference's tie rule (lowest index, native/kernels/sm120/sampling.cu:26,
+ * 80), writes tokens and values [n_rows], and finally advances *d_step. */
+MC_SM100_API mc_status_t mc_sm100_peer_argmax(const float* d_val, const int32_t* d_idx, uint32_t n_rows,
                                               const uint64_t* d_pair_peers, const uint64_t* d_flag_peers,
                                               const uint64_t* d_my_pairs, const uint32_t* d_my_flags,
                                               uint32_t* d_step, uint32_t rank, uint32_t world,

@@ -71,7 +71,8 @@ SIGNATURES = {
     "mc_sm100_gemv_sharded": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _vp, _vp, _i32]),
     "mc_sm100_lm_head_argmax_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _i32,
                                                _vp, _vp, _vp, _vp, _vp, _i32]),
-    "mc_sm100_peer_argmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_peer_argmax": (_i32, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_peer_allgather_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _i32]),
     "mc_sm100_peer_allgather": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _u32, C.c_uint64, _vp, _vp, _i32]),
     "mc_sm100_wpk_name_hash": (C.c_uint64, [C.c_char_p]),
     "mc_sm100_wpk_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
@@ -371,8 +372,8 @@ def lm_head_argmax_sharded(w, scale, res_in, addend, norm_w, res_out, logits, N,
 
 
 def peer_argmax(val, idx, pair_peers, flag_peers, my_pairs, my_flags, step, rank, world, status, token, token_val=None,
-                timeout_ns=0, stream=None, pdl=False):
-    _check(lib().mc_sm100_peer_argmax(_p(val), _p(idx), _p(pair_peers), _p(flag_peers), _p(my_pairs), _p(my_flags),
+                timeout_ns=0, stream=None, pdl=False, n_rows=1):
+    _check(lib().mc_sm100_peer_argmax(_p(val), _p(idx), n_rows, _p(pair_peers), _p(flag_peers), _p(my_pairs), _p(my_flags),
                                       _p(step), rank, world, timeout_ns, _p(status), _p(token), _p(token_val),
                                       _stream(stream), int(pdl)))
 
@@ -439,6 +440,13 @@ def e4m3_from_f32_host(values):
 def wpk_upload(h, name, row_lo, row_hi, interleave, dst, scale_dst=None, stream=None):
     _check(lib().mc_sm100_wpk_upload(h, name.encode(), row_lo, row_hi, int(interleave), _p(dst),
                                      dst.numel() * dst.element_size(), _p(scale_dst), _stream(stream)))
+
+
+def peer_allgather_rows(shard, rows, row_bytes, dst_pitch_bytes, slot_bytes, peer_bufs, peer_flags, my_flags, epoch, rank, world,
+                        timeout_ns=0, status=None, stream=None, pdl=False):
+    _check(lib().mc_sm100_peer_allgather_rows(_p(shard), rows, row_bytes, dst_pitch_bytes, slot_bytes, _p(peer_bufs), _p(peer_flags),
+                                              _p(my_flags), _p(epoch), rank, world, timeout_ns, _p(status),
+                                              _stream(stream), int(pdl)))
 
 
 def peer_allgather(shard, shard_bytes, slot_bytes, peer_bufs, peer_flags, my_flags, epoch, rank, world,

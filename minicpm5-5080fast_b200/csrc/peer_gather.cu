@@ -17,8 +17,10 @@ namespace mcl {
 
 constexpr unsigned long long kPeerWaitDefaultNs = 1000ull * 1000ull * 1000ull;   // 1 s
 
+// rows x row_units (16-byte units) from a contiguous shard to column slot `rank` of every peer's
+// buffer, whose rows are pitch_units apart (rows = 1: the plain 1-D gather).
 __global__ void __launch_bounds__(512, 1)
-peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t units, uint32_t slot_units,
+peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t rows, uint32_t row_units, uint32_t pitch_units, uint32_t slot_units,
                       const uint64_t* __restrict__ peer_bufs, const uint64_t* __restrict__ peer_flags,
                       uint32_t* my_flags, uint32_t* epoch, uint32_t rank, uint32_t world,
                       unsigned long long limit_ns, int32_t* status) {
@@ -29,9 +31,13 @@ peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t units, uint32_t 
     if (threadIdx.x == 0) { s_epoch = *epoch + 1u; s_fail = 0; }
     __syncthreads();
     const uint32_t e = s_epoch;
+    const uint32_t units = rows * row_units;
     for (uint32_t p = 0; p < world; ++p) {
         uint4* dst = reinterpret_cast<uint4*>(peer_bufs[p]) + (size_t)rank * slot_units;
-        for (uint32_t i = threadIdx.x; i < units; i += blockDim.x) dst[i] = shard[i];
+        for (uint32_t i = threadIdx.x; i < units; i += blockDim.x) {
+            const uint32_t m = i / row_units, c = i - m * row_units;
+            dst[(size_t)m * pitch_units + c] = shard[i];
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -64,20 +70,30 @@ peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t units, uint32_t 
 
 using namespace mcl;
 
+extern "C" mc_status_t mc_sm100_peer_allgather_rows(const void* d_shard, uint32_t rows, uint32_t row_bytes, uint32_t dst_pitch_bytes,
+                                                    uint32_t slot_bytes, const uint64_t* d_peer_bufs, const uint64_t* d_peer_flags,
+                                                    uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank, uint32_t world,
+                                                    uint64_t timeout_ns, int32_t* d_status, void* stream, int32_t pdl) {
+    clear_error();
+    if (d_shard == nullptr || d_peer_bufs == nullptr || d_peer_flags == nullptr || d_my_flags == nullptr ||
+        d_epoch == nullptr || world == 0 || world > 64u || rank >= world || rows == 0 || (row_bytes & 15u) != 0 ||
+        (slot_bytes & 15u) != 0 || (dst_pitch_bytes & 15u) != 0 || row_bytes > slot_bytes ||
+        (rows > 1u && (uint64_t)rank * slot_bytes + row_bytes > dst_pitch_bytes) || !aligned16(d_shard)) {
+        set_error("mc_sm100_peer_allgather: invalid args (rank=%u world=%u rows=%u row=%u slot=%u pitch=%u)", rank, world, rows,
+                  row_bytes, slot_bytes, dst_pitch_bytes);
+        return MC_E_INVALID_ARGUMENT;
+    }
+    (void)launch(peer_allgather_kernel, dim3(1), dim3(512), 0, (cudaStream_t)stream, pdl != 0, (const uint4*)d_shard, rows,
+                 row_bytes / 16u, dst_pitch_bytes / 16u, slot_bytes / 16u, d_peer_bufs, d_peer_flags, d_my_flags, d_epoch, rank, world,
+                 (unsigned long long)(timeout_ns ? timeout_ns : kPeerWaitDefaultNs), d_status);
+    MCL_CHECK_LAUNCH("peer_allgather");
+    return MC_OK;
+}
+
 extern "C" mc_status_t mc_sm100_peer_allgather(const void* d_shard, uint32_t shard_bytes, uint32_t slot_bytes,
                                                const uint64_t* d_peer_bufs, const uint64_t* d_peer_flags,
                                                uint32_t* d_my_flags, uint32_t* d_epoch, uint32_t rank, uint32_t world,
                                                uint64_t timeout_ns, int32_t* d_status, void* stream, int32_t pdl) {
-    clear_error();
-    if (d_shard == nullptr || d_peer_bufs == nullptr || d_peer_flags == nullptr || d_my_flags == nullptr ||
-        d_epoch == nullptr || world == 0 || world > 64u || rank >= world || (shard_bytes & 15u) != 0 ||
-        (slot_bytes & 15u) != 0 || shard_bytes > slot_bytes || !aligned16(d_shard)) {
-        set_error("mc_sm100_peer_allgather: invalid args (rank=%u world=%u shard=%u slot=%u)", rank, world, shard_bytes, slot_bytes);
-        return MC_E_INVALID_ARGUMENT;
-    }
-    (void)launch(peer_allgather_kernel, dim3(1), dim3(512), 0, (cudaStream_t)stream, pdl != 0, (const uint4*)d_shard,
-                 shard_bytes / 16u, slot_bytes / 16u, d_peer_bufs, d_peer_flags, d_my_flags, d_epoch, rank, world,
-                 (unsigned long long)(timeout_ns ? timeout_ns : kPeerWaitDefaultNs), d_status);
-    MCL_CHECK_LAUNCH("peer_allgather");
-    return MC_OK;
+    return mc_sm100_peer_allgather_rows(d_shard, 1u, shard_bytes, 0u, slot_bytes, d_peer_bufs, d_peer_flags, d_my_flags, d_epoch, rank,
+                                        world, timeout_ns, d_status, stream, pdl);
 }

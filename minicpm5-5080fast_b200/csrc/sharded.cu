@@ -15,27 +15,32 @@
 
 namespace mcl {
 
-// One warp.  Lane p < world talks to rank p.
-__global__ void __launch_bounds__(32, 1)
-peer_argmax_kernel(const float* __restrict__ val, const int32_t* __restrict__ idx, const uint64_t* __restrict__ pair_peers,
-                   const uint64_t* __restrict__ flag_peers, const uint64_t* my_pairs, const uint32_t* my_flags,
-                   uint32_t* step, uint32_t rank, uint32_t world, unsigned long long limit_ns, int32_t* status,
-                   int32_t* token, float* token_val) {
+// One CTA.  Every rank pushes the (value, index) of each of its n_rows shard results to every rank
+// (pair slots laid out [world][n_rows]), signals, waits -- bounded -- for the others, then reduces
+// each row over the ranks with the reference's tie rule and advances *step.
+__global__ void __launch_bounds__(256, 1)
+peer_argmax_kernel(const float* __restrict__ val, const int32_t* __restrict__ idx, uint32_t n_rows,
+                   const uint64_t* __restrict__ pair_peers, const uint64_t* __restrict__ flag_peers, const uint64_t* my_pairs,
+                   const uint32_t* my_flags, uint32_t* step, uint32_t rank, uint32_t world, unsigned long long limit_ns,
+                   int32_t* status, int32_t* token, float* token_val) {
+    __shared__ uint32_t s_step;
+    __shared__ int s_ok;
     pdl_trigger();
     pdl_wait();
-    const uint32_t lane = threadIdx.x;
-    const uint32_t s = *step;
-    float bv = -INFINITY;
-    int32_t bi = INT32_MAX;
-    if (lane < world) {
-        const uint64_t packed = (uint64_t)__float_as_uint(val[0]) | ((uint64_t)(uint32_t)idx[0] << 32);
-        uint64_t* dst = reinterpret_cast<uint64_t*>(pair_peers[lane]) + rank;
-        *reinterpret_cast<volatile uint64_t*>(dst) = packed;
-        __threadfence_system();
-        const uint64_t f = flag_peers[lane] + 4ull * rank;
+    if (threadIdx.x == 0) { s_step = *step; s_ok = 1; }
+    __syncthreads();
+    const uint32_t s = s_step;
+    for (uint32_t i = threadIdx.x; i < world * n_rows; i += blockDim.x) {
+        const uint32_t p = i / n_rows, m = i - p * n_rows;
+        const uint64_t packed = (uint64_t)__float_as_uint(val[m]) | ((uint64_t)(uint32_t)idx[m] << 32);
+        *reinterpret_cast<volatile uint64_t*>(reinterpret_cast<uint64_t*>(pair_peers[p]) + (size_t)rank * n_rows + m) = packed;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const uint64_t f = flag_peers[threadIdx.x] + 4ull * rank;
         asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(f), "r"(1u) : "memory");
-        // rank `lane`'s pair of this step
-        const uint32_t* mine = my_flags + lane;
+        const uint32_t* mine = my_flags + threadIdx.x;
         unsigned long long t0 = 0;
         bool ok = *reinterpret_cast<volatile int32_t*>(status) == 0;
         for (uint32_t spin = 0; ok; ++spin) {
@@ -48,24 +53,24 @@ peer_argmax_kernel(const float* __restrict__ val, const int32_t* __restrict__ id
                 else if (now - t0 > limit_ns) { *reinterpret_cast<volatile int32_t*>(status) = 1; ok = false; }
             }
         }
-        if (ok) {
-            const uint64_t got = *reinterpret_cast<const volatile uint64_t*>(my_pairs + lane);
-            bv = __uint_as_float((uint32_t)got);
-            bi = (int32_t)(uint32_t)(got >> 32);
-            if (bv != bv) { bv = -INFINITY; bi = INT32_MAX; }
+        if (!ok) s_ok = 0;
+    }
+    __syncthreads();
+    for (uint32_t m = threadIdx.x; m < n_rows; m += blockDim.x) {
+        float bv = -INFINITY;
+        int32_t bi = INT32_MAX;
+        if (s_ok) {
+            for (uint32_t r = 0; r < world; ++r) {
+                const uint64_t got = *reinterpret_cast<const volatile uint64_t*>(my_pairs + (size_t)r * n_rows + m);
+                const float v = __uint_as_float((uint32_t)got);
+                const int32_t i = (int32_t)(uint32_t)(got >> 32);
+                if (v == v && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+            }
         }
+        token[m] = bi;
+        if (token_val != nullptr) token_val[m] = bv;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) {
-        *token = bi;
-        if (token_val != nullptr) *token_val = bv;
-        *step = s + 1u;
-    }
+    if (threadIdx.x == 0) *step = s + 1u;
 }
 
 }  // namespace mcl
@@ -99,18 +104,18 @@ mc_status_t mc_sm100_gemv_sharded(int32_t prologue, int32_t epilogue, const void
                    : launch_fast<1>(pro, epi, a, (cudaStream_t)stream, pdl != 0);
 }
 
-mc_status_t mc_sm100_peer_argmax(const float* d_val, const int32_t* d_idx, const uint64_t* d_pair_peers,
+mc_status_t mc_sm100_peer_argmax(const float* d_val, const int32_t* d_idx, uint32_t n_rows, const uint64_t* d_pair_peers,
                                  const uint64_t* d_flag_peers, const uint64_t* d_my_pairs, const uint32_t* d_my_flags,
                                  uint32_t* d_step, uint32_t rank, uint32_t world, uint64_t timeout_ns,
                                  int32_t* d_status, int32_t* d_token, float* d_token_val, void* stream, int32_t pdl) {
     clear_error();
     if (d_val == nullptr || d_idx == nullptr || d_pair_peers == nullptr || d_flag_peers == nullptr ||
         d_my_pairs == nullptr || d_my_flags == nullptr || d_step == nullptr || d_status == nullptr ||
-        d_token == nullptr || world == 0 || world > 32u || rank >= world) {
-        set_error("mc_sm100_peer_argmax: invalid args (rank=%u world=%u)", rank, world);
+        d_token == nullptr || world == 0 || world > 32u || rank >= world || n_rows == 0 || n_rows > 64u) {
+        set_error("mc_sm100_peer_argmax: invalid args (rank=%u world=%u rows=%u)", rank, world, n_rows);
         return MC_E_INVALID_ARGUMENT;
     }
-    (void)launch(peer_argmax_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, pdl != 0, d_val, d_idx, d_pair_peers,
+    (void)launch(peer_argmax_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, pdl != 0, d_val, d_idx, n_rows, d_pair_peers,
                  d_flag_peers, d_my_pairs, d_my_flags, d_step, rank, world,
                  (unsigned long long)(timeout_ns ? timeout_ns : kShardWaitDefaultNs), d_status, d_token, d_token_val);
     MCL_CHECK_LAUNCH("peer_argmax");

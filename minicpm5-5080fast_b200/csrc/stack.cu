@@ -104,7 +104,8 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
     s.qkv = take(M * d->qkv_rows * 2); s.ctx = take(M * H * 2); s.o = take(M * H * 2);
     s.mid = take(M * (size_t)d->inter * 2); s.down = take(M * H * 2); s.logits = take(M * (size_t)d->vocab * 2);
     s.stage = take(mc_sm100_argmax_stage_bytes(d->max_batch)); s.tokens = take(M * 4); s.vals = take(M * 4);
-    s.sync = take(256);   // sharded: [0] step counter, [1] failure word, [2] shard token, [16..] peer address tables
+    s.sync = take(1024);  // sharded: words [0] step counter, [1] failure word, [2] shard token, [3] shard value, [5] gather epoch;
+                          // peer address tables (8 x u64 each) at bytes 64 pairs, 128 pair counters, 256.. batched buffers
     s.total = off;
     return s;
 }
@@ -114,9 +115,12 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
 // their arrival counters.
 enum : uint32_t { XK_QKV = 0, XK_O = 1, XK_MID = 2, XK_DOWN = 3, XK_VECS = 4 };
 struct Exchange {
-    size_t buf[XK_VECS];     // gathered qkv, o, mid, down
-    uint32_t pitch[XK_VECS]; // slot pitch in words
-    size_t pairs, pair_flags;   // 8 x 8 bytes, 8 x uint32
+    size_t buf[XK_VECS];     // gathered qkv, o, mid, down (tagged words, M = 1)
+    uint32_t pitch[XK_VECS]; // slot pitch in elements (the same for the batched buffers)
+    size_t pairs, pair_flags;   // [8][max_batch] x 8 bytes, 8 x uint32
+    // batched steps (M > 1): plain bf16 [max_batch, full width] activations + the gather's arrival flags
+    size_t bbuf[XK_VECS], bflags;
+    uint32_t width[XK_VECS];
     size_t bytes;
 };
 static Exchange make_exchange(const mc_sm100_stack_desc_t* d) {
@@ -126,11 +130,16 @@ static Exchange make_exchange(const mc_sm100_stack_desc_t* d) {
     size_t off = 0;
     for (uint32_t k = 0; k < XK_VECS; ++k) {
         x.pitch[k] = shard_span(dims[k], W, 0).pitch;
+        x.width[k] = dims[k];
         x.buf[k] = off;
         off += align256((size_t)x.pitch[k] * W * 4u);
     }
-    x.pairs = off; off += align256(8u * 8u);
+    x.pairs = off; off += align256(8u * 8u * (size_t)d->max_batch);
     x.pair_flags = off; off += align256(8u * 4u);
+    if (d->max_batch > 1u) {
+        for (uint32_t k = 0; k < XK_VECS; ++k) { x.bbuf[k] = off; off += align256((size_t)d->max_batch * dims[k] * 2u); }
+        x.bflags = off; off += align256(8u * 4u);
+    }
     x.bytes = off;
     return x;
 }
@@ -216,10 +225,83 @@ static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int
     STEP(mc_sm100_lm_head_argmax_sharded(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), res_in,
                                          gathered(XK_DOWN), (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), rb, logits, sv.rows, H,
                                          d.eps, (int32_t)sv.lo, st->s + st->scr.stage, shard_tok, shard_val, &q, sp, 1));
-    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, reinterpret_cast<const uint64_t*>(sync + 16),
+    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, 1u, reinterpret_cast<const uint64_t*>(sync + 16),
                               reinterpret_cast<const uint64_t*>(sync + 32), reinterpret_cast<const uint64_t*>(own + x.pairs),
                               reinterpret_cast<const uint32_t*>(own + x.pair_flags), sync, R, W, st->timeout_ns,
                               reinterpret_cast<int32_t*>(sync + 1), d_tokens, reinterpret_cast<float*>(st->s + st->scr.vals), sp, 1));
+#undef STEP
+    return MC_OK;
+}
+
+// Sharded batched step (M > 1): every rank runs the batched chain on its rows of each matrix; the
+// [M, rows] result of a linear is scattered into column slot `rank` of every rank's [M, width]
+// buffer by one small kernel per linear (mc_sm100_peer_allgather_rows), which is then the activation
+// of the next GEMM.  The residual stream and the norms are computed redundantly on every rank.
+static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, cudaStream_t stream) {
+    const mc_sm100_stack_desc_t& d = st->desc;
+    const uint32_t W = d.world, R = d.rank, H = d.hidden, I = d.inter, L = d.layers;
+    if (st->peer[R] == 0) { set_error("stack step: sharded stack without a bound exchange region"); return MC_E_INVALID_ARGUMENT; }
+    if ((d.qkv_rows | H | I) & 7u) { set_error("stack step: sharded batched steps need widths that are multiples of 8"); return MC_E_UNSUPPORTED; }
+    const bool fp8 = d.precision == 2u;
+    const Exchange& x = st->xch;
+    const uint64_t own = st->peer[R];
+    const Span sq = shard_span(d.qkv_rows, W, R), sh = shard_span(H, W, R), si = shard_span(I, W, R), sv = shard_span(d.vocab, W, R);
+    uint32_t* sync = reinterpret_cast<uint32_t*>(st->s + st->scr.sync);
+    uint8_t* sync_b = reinterpret_cast<uint8_t*>(sync);
+    int32_t* status = reinterpret_cast<int32_t*>(sync + 1);
+    auto buf = [&](size_t off) { return reinterpret_cast<uint16_t*>(st->s + off); };
+    uint16_t *ra = buf(st->scr.res_a), *h = buf(st->scr.h), *ctx = buf(st->scr.ctx), *logits = buf(st->scr.logits);
+    uint16_t* part = buf(I >= d.qkv_rows ? st->scr.mid : st->scr.qkv);      // this rank's [M, rows] result of the current linear
+    auto full = [&](uint32_t k) { return reinterpret_cast<uint16_t*>(own + x.bbuf[k]); };
+    void* sp = (void*)stream;
+    mc_status_t rc = MC_OK;
+#define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
+    // this rank's [M, rows] result (contiguous in `part`) -> column slot of every rank's buffer k
+    auto gather = [&](uint32_t k, uint32_t rows) {
+        return mc_sm100_peer_allgather_rows(part, M, rows * 2u, x.width[k] * 2u, x.pitch[k] * 2u,
+                                            reinterpret_cast<const uint64_t*>(sync_b + 256u + 64u * k),
+                                            reinterpret_cast<const uint64_t*>(sync_b + 512u),
+                                            reinterpret_cast<uint32_t*>(own + x.bflags), sync + 5, R, W, st->timeout_ns, status, sp, 1);
+    };
+    auto linear = [&](uint32_t l, uint32_t wsec, uint32_t ssec, const uint16_t* in, uint32_t rows, uint32_t K) {
+        return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, l, wsec), (const float*)sec(st, l, ssec), in, part, M, rows, K, sp, 1)
+                   : mc_sm100_gemm_bf16(sp, nullptr, 0, M, rows, K, sec(st, l, wsec), in, part);
+    };
+    cudaError_t e = cudaMemcpyAsync(ra, d_x, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    const uint16_t* addend = nullptr;
+    for (uint32_t l = 0; l < L; ++l) {
+        STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps, sp, 1));
+        STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, sq.rows, H));
+        STEP(gather(XK_QKV, sq.rows));
+        e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, full(XK_QKV), (size_t)d.qkv_rows * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+        STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, sh.rows, H));
+        STEP(gather(XK_O, sh.rows));
+        STEP(mc_sm100_residual_rmsnorm_rows(ra, full(XK_O), (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
+        STEP(mc_sm100_gate_up_swiglu(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), h, part, M, 2u * si.rows, H, sp, 1));
+        STEP(gather(XK_MID, si.rows));
+        STEP(linear(l, SEC_DOWN, SEC_DOWN_SCALE, full(XK_MID), sh.rows, I));
+        STEP(gather(XK_DOWN, sh.rows));
+        addend = full(XK_DOWN);
+    }
+    STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), h, M, H, d.eps, sp, 1));
+    void* stage = st->s + st->scr.stage;
+    int32_t* shard_tok = reinterpret_cast<int32_t*>(st->s + st->scr.tokens);
+    float* shard_val = reinterpret_cast<float*>(st->s + st->scr.vals);
+    if (M <= 8u) {
+        STEP(mc_sm100_lm_head_argmax(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, sv.rows, M, sv.rows, H,
+                                     (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
+    } else {
+        rc = fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, M, sv.rows, H, sp, 1)
+                 : mc_sm100_gemm_bf16(sp, nullptr, 0, M, sv.rows, H, sec(st, 0, SEC_LM_HEAD), h, logits);
+        if (rc != MC_OK) return rc;
+        STEP(mc_sm100_argmax_bf16(logits, M, sv.rows, sv.rows, (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
+    }
+    // per-row (value, index) of every rank -> tokens; the winning values land in the (otherwise unused) o scratch
+    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, M, reinterpret_cast<const uint64_t*>(sync + 16), reinterpret_cast<const uint64_t*>(sync + 32),
+                              reinterpret_cast<const uint64_t*>(own + x.pairs), reinterpret_cast<const uint32_t*>(own + x.pair_flags), sync, R, W,
+                              st->timeout_ns, status, d_tokens, reinterpret_cast<float*>(st->s + st->scr.o), sp, 1));
 #undef STEP
     return MC_OK;
 }
@@ -237,10 +319,7 @@ static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M,
     float* vals = reinterpret_cast<float*>(st->s + st->scr.vals);
     void* sp = (void*)stream;
     mc_status_t rc = MC_OK;
-    if (d.world > 1u) {
-        if (M != 1) { set_error("stack step: a sharded stack serves M = 1 (got %u)", M); return MC_E_UNSUPPORTED; }
-        return run_step_sharded(st, d_x, d_tokens, stream);
-    }
+    if (d.world > 1u) return M == 1 ? run_step_sharded(st, d_x, d_tokens, stream) : run_step_sharded_batched(st, d_x, M, d_tokens, stream);
 #define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
     if (M == 1) {
         // fused chain: residual add + RMSNorm live in the GEMV prologues, SwiGLU in the gate_up epilogue
@@ -366,13 +445,18 @@ mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t st, const uint64_t* h_
     for (auto& g : st->graph)
         if (g != nullptr) { cudaGraphExecDestroy(g); g = nullptr; }
     const cudaStream_t s = (cudaStream_t)stream;
-    uint32_t words[64] = {0};
-    words[0] = 1u;   // step counter starts at 1; [1] failure word = 0
-    uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);
+    uint32_t words[256] = {0};
+    words[0] = 1u;   // step counter starts at 1; [1] failure word = 0; [5] gather epoch = 0
+    uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);          // byte 64: pairs, byte 128: pair counters
+    uint64_t* btables = reinterpret_cast<uint64_t*>(words + 64);         // byte 256 + 64 k: batched buffer k; byte 512: gather flags
     for (uint32_t p = 0; p < W; ++p) {
         st->peer[p] = h_peer_addrs[p];
         tables[p] = h_peer_addrs[p] + st->xch.pairs;
         tables[8 + p] = h_peer_addrs[p] + st->xch.pair_flags;
+        if (st->desc.max_batch > 1u) {
+            for (uint32_t k = 0; k < XK_VECS; ++k) btables[8u * k + p] = h_peer_addrs[p] + st->xch.bbuf[k];
+            btables[8u * XK_VECS + p] = h_peer_addrs[p] + st->xch.bflags;
+        }
     }
     st->timeout_ns = timeout_ns;
     cudaError_t e = cudaMemsetAsync(reinterpret_cast<void*>(st->peer[R]), 0, st->xch.bytes, s);

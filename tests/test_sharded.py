@@ -218,6 +218,63 @@ def test_peer_argmax_reduces_pairs(pkg, g):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fp8", [False, True])
+def test_sharded_batched_stack_two_gpus(pkg, g, fp8):
+    """M = 8 on two GPUs: per-linear scatter into every rank's [M, width] buffers; logits within tolerance of one GPU."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29743", os.path.join(ROOT, "tests", "sharded_worker.py"), "--rows", "8"] + (["--fp8"] if fp8 else [])
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "SHARDED-OK" in out.stdout, out.stdout[-2000:]
+
+
+@pytest.mark.gpu
+def test_peer_allgather_rows_and_batched_argmax(pkg, g):
+    """One GPU, world of two played in sequence: 2-D scatter into both 'ranks' buffers, then the M-row pair reduce."""
+    import torch
+    M, width, pitch = 3, 40, 24                      # rank 0 owns columns [0, 24), rank 1 [24, 40)
+    bufs = [torch.zeros((M, width), dtype=torch.int16, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    epochs = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tb = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    tf = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device="cuda")
+    shards = [torch.arange(M * 24, dtype=torch.int16, device="cuda").reshape(M, 24) + 100,
+              torch.arange(M * 16, dtype=torch.int16, device="cuda").reshape(M, 16) + 1000]
+    # rank 1 first with a short limit: rank 0 has not delivered -> bounded wait runs out, data still lands
+    pkg.peer_allgather_rows(shards[1], M, 32, width * 2, pitch * 2, tb, tf, flags[1], epochs[1], 1, 2, timeout_ns=2_000_000, status=status)
+    g.sync()
+    assert status.item() == 1
+    status.zero_()
+    pkg.peer_allgather_rows(shards[0], M, 48, width * 2, pitch * 2, tb, tf, flags[0], epochs[0], 0, 2, status=status)
+    g.sync()
+    assert status.item() == 0
+    want = torch.cat((shards[0], shards[1]), dim=1)
+    assert torch.equal(bufs[0], want) and torch.equal(bufs[1], want)
+    # M-row greedy reduce: this process plays rank 0 of two, rank 1's pairs are already there
+    pairs = torch.zeros(2 * M, dtype=torch.int64, device="cuda")
+    pflags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    step = torch.ones(1, dtype=torch.int32, device="cuda")
+    other_v, other_i = [0.5, 3.0, -1.0], [900, 901, 902]
+    for m in range(M):
+        pairs[M + m] = int(np.float32(other_v[m]).view(np.uint32)) | (other_i[m] << 32)
+    pflags[1] = 1
+    tp = torch.tensor([pairs.data_ptr()] * 2, dtype=torch.int64, device="cuda")
+    tfl = torch.tensor([pflags.data_ptr()] * 2, dtype=torch.int64, device="cuda")
+    val = torch.tensor([1.5, 3.0, -2.0], dtype=torch.float32, device="cuda")
+    idx = torch.tensor([10, 11, 12], dtype=torch.int32, device="cuda")
+    tok = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    tv = torch.zeros(M, dtype=torch.float32, device="cuda")
+    pkg.peer_argmax(val, idx, tp, tfl, pairs, pflags, step, 0, 2, status, tok, tv, n_rows=M)
+    g.sync()
+    assert tok.tolist() == [10, 11, 902] and tv.tolist() == [1.5, 3.0, -1.0] and step.item() == 2 and status.item() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True])
 def test_sharded_stack_two_gpus(pkg, g, fp8):
     """One process per GPU: tokens and logits of the sharded stack equal the one-GPU stack's."""
     import torch
