@@ -35,6 +35,7 @@ namespace {
 constexpr int kTileN = 128;        // weight rows per CTA (MMA M)
 constexpr int kThreads = 320;      // 10 warps
 constexpr int kConvThreads = 256;  // warps 2..9
+constexpr uint32_t kConvGroup = 128;  // converter threads that share one K block (two groups; four groups of 64 ran into bounded-wait timeouts and are not used)
 constexpr int kRowBytes = 128;     // bytes per operand-tile row in shared memory (one swizzle row)
 constexpr unsigned long long kWaitLimitNs = 200ull * 1000ull * 1000ull;   // a wait gives up after 200 ms
 
@@ -195,9 +196,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (uint32_t s = 0; s < 8; ++s) {
             mbar_init(op_full(s), 1);
             mbar_init(op_empty(s), 1);
-            mbar_init(conv_done(s), kConvThreads);
+            mbar_init(conv_done(s), kConvGroup);
             mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), kConvThreads);
+            mbar_init(raw_empty(s), kConvGroup);
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -293,16 +294,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // ---------------------------------------------------------------- e4m3 -> bf16 widening
         // thread -> (row, 16-byte raw chunk): a quarter warp covers 8 rows of one chunk column, which
         // makes the swizzled 16-byte stores of the operand tile bank-conflict free.
-        const uint32_t ct = tid - 64u;
+        // The eight warps work as groups of kConvGroup threads on alternate K blocks, so that several blocks are in
+        // the (latency-bound) load -> place bits -> store -> fence chain at any time.
+        const uint32_t ct = (tid - 64u) & (kConvGroup - 1u), group = (tid - 64u) / kConvGroup;
         bool ok = true;
-        for (uint32_t it = 0; it < nloc && ok; ++it) {
+        for (uint32_t it = group; it < nloc && ok; it += kConvThreads / kConvGroup) {
             const uint32_t sr = it % RAWS, so = it % OPS;
             ok = mbar_wait(raw_full(sr), (it / RAWS) & 1u, abortp);
             if (ok && it >= OPS) ok = mbar_wait(op_empty(so), ((it / OPS) - 1u) & 1u, abortp);
             if (!ok) break;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const uint32_t c = ct + kConvThreads * i;            // 0..511
+            for (int i = 0; i < 512 / (int)kConvGroup; ++i) {
+                const uint32_t c = ct + kConvGroup * i;              // 0..511
                 const uint32_t row = (c & 7u) | ((c >> 5) << 3), cc = (c >> 3) & 3u;
                 uint4 v;
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
