@@ -10,9 +10,17 @@ weight stream (per layer: fused qkv 2304->3456, o 2304->2304, gate_up
 greedy argmax) on seeded synthetic weights, M activation rows (default 1).  The
 metric is the HBM throughput of that stream: algorithmic bytes (every weight,
 scale, input and output counted once) divided by device time.  With N > 1 the
-matrices are sharded along N (output rows) over the ranks, outputs are
-all-gathered with NCCL after every linear, and the aggregate over all ranks is
-reported (strong scaling: the total work is fixed).
+matrices are sharded along N (output rows) over the ranks, every output is
+exchanged inside the producing kernel (peer stores over NVLink; NCCL only for
+rendezvous and barriers), and the aggregate over all ranks is reported (strong
+scaling: the total work is fixed).
+
+What is timed is also checked: the token of the graph replay must equal the
+eager step's, the logits must match a plain fp32 PyTorch statement of the same
+chain on the same weights, and with N > 1 rank 0 also runs the one-GPU stack
+and compares token and logits shard with the sharded run.  A mismatch exits
+non-zero without a JSON line.  After the headline the default run measures the
+single-linear configurations (one entry each under "configs").
 
 `--impl reference` times the reference's own CPU implementation of the same
 linears (its native cross-check compiled in place under oracle/_ref for bf16;
@@ -35,6 +43,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 L, H, QKV, I, V = 40, 2304, 3456, 5760, 122753
+if os.environ.get("MC_LAYERS"):          # profiler captures only: a shorter stack keeps the capture small
+    L = int(os.environ["MC_LAYERS"])
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -138,7 +148,8 @@ def cpu_reference(dtype, m, budget_s, steps=1, warmup=0):
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle_np as onp
-    shapes = [(QKV, H), (H, H), (2 * I, H), (H, I)]
+    # 1/40 of the stream: one layer's four linears and one fortieth of the lm_head rows
+    shapes = [(QKV, H), (H, H), (2 * I, H), (H, I), ((V + L - 1) // L, H)]
     wb = 2 if dtype == "bf16" else 1
     sample_bytes = sum(linear_bytes(n, k, m, wb, n // 2 if i == 2 else n) for i, (n, k) in enumerate(shapes))
     ws = [onp.seeded_bf16(50 + i, s, 0.02) for i, s in enumerate(shapes)]
@@ -186,9 +197,37 @@ def cpu_reference(dtype, m, budget_s, steps=1, warmup=0):
             break
     per = dt / n
     info = {"value": sample_bytes / per / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
-            "sample": f"one layer (qkv, o, gate_up, down) of the stream, M={m}, {n} passes, {per * 1e3:.1f} ms per pass",
-            "ms_per_pass": per * 1e3}
+            "sample": f"1/40 of the stream (one layer: qkv, o, gate_up, down; {shapes[4][0]} of the lm_head rows), M={m}, {n} passes, {per * 1e3:.1f} ms per pass",
+            "ms_per_pass": per * 1e3, "cpu_model": cpu_model()}
+    if budget_s > 0:
+        # second CPU figure: the reference's numpy statement (tools/reference_forward.py:158-172 restated in
+        # oracle_np: upcast W and x to fp32 on every call, BLAS matmul, round to bf16) on the same sample
+        qs2 = [onp.make_fp8_weight(w) for w in ws] if dtype == "fp8" else None
+
+        def run_np():
+            for i, (w, x) in enumerate(zip(ws, xs)):
+                onp.linear_fp8(qs2[i][0], qs2[i][1], x) if dtype == "fp8" else onp.linear_bf16(w, x)
+        run_np()
+        t0, k = time.perf_counter(), 0
+        while True:
+            run_np()
+            k += 1
+            dtn = time.perf_counter() - t0
+            if dtn >= min(3.0, budget_s):
+                break
+        info["numpy"] = {"value": sample_bytes / (dtn / k) / 1e9, "unit": "GB/s", "threads": os.cpu_count() or 1,
+                         "ms_per_pass": dtn / k * 1e3, "what": "numpy fp32 matmul with per-call upcast of W, same sample"}
     return info
+
+
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 def run_reference(args):
@@ -215,7 +254,7 @@ def workload_name(args):
         extra = {0: "", 1: " + SwiGLU epilogue", 2: " + fused argmax"}[kind]
         w8 = ", W8A8 (activations quantised per row)" if args.dtype == "fp8" and args.m > 1 and os.environ.get("MC_W8A8", "0") == "1" else ""
         return f"single linear {args.workload} {k}->{n}{extra}, {args.dtype}{w8}, M={args.m}, rotating weight copies"
-    return (f"config5 full 40-layer decode weight stream (qkv 2304->3456, o 2304->2304, gate_up 2304->11520 + SwiGLU, "
+    return (f"config5 full {L}-layer decode weight stream (qkv 2304->3456, o 2304->2304, gate_up 2304->11520 + SwiGLU, "
             f"down 5760->2304, lm_head 2304->122753 + argmax), {args.dtype}, M={args.m}")
 
 
@@ -308,7 +347,9 @@ class Stream:
         z = lambda *s: torch.zeros(s, dtype=torch.int16, device=dev)
         self.per = {"qkv": shard_rows(QKV, world, 0)[2], "o": shard_rows(H, world, 0)[2],
                     "mid": shard_rows(I, world, 0)[2], "down": shard_rows(H, world, 0)[2]}
-        self.x_in = z(m, H)
+        gx = torch.Generator(device="cpu")
+        gx.manual_seed(20260908 + 5999)           # the same activation on every rank
+        self.x_in = torch.randn((m, H), generator=gx).to(torch.bfloat16).view(torch.int16).to(dev)
         self.res = [z(m, H), z(m, H)]
         self.qkv_s, self.qkv = z(m, self.per["qkv"]), z(world, m, self.per["qkv"])
         self.o_s, self.o = z(m, self.per["o"]), z(world, m, self.per["o"])
@@ -336,6 +377,40 @@ class Stream:
             self.ctx = z(m, H)
             self.qkv_m, self.o_m, self.mid_m, self.dn_m = z(m, QKV), z(m, H), z(m, I), z(m, H)
             self.logits = z(m, V)
+
+    def logits_view(self):
+        """The bf16 logits [M, rows of this rank's vocab shard] the last step of the stack wrote."""
+        if self.handle is None:
+            return self.logits[:, :self.v_rows]
+        off = self.pkg.stack_logits_ptr(self.handle) - self.scratch.data_ptr()
+        n = self.m * self.v_rows
+        return self.scratch[off:off + 2 * n].view(self.torch.int16).view(self.m, self.v_rows)
+
+    def reference_logits(self, x_bits):
+        """Plain PyTorch fp32 statement of the same chain on the same device-resident weights (one GPU):
+        every stored intermediate rounded to bf16 where the library stores bf16.  The checker, never timed."""
+        torch = self.torch
+        assert self.world == 1
+        bf = lambda t: t.to(torch.bfloat16).to(torch.float32)
+        bits = lambda t: t.view(torch.bfloat16).to(torch.float32)
+
+        def lin(ws, v):
+            w, sc = ws
+            if sc is None:
+                return bf(v @ bits(w).T)
+            return bf((v @ w.view(torch.float8_e4m3fn).to(torch.float32).T) * sc[None, :])
+
+        def rms(v, nw):
+            return bf(v * torch.rsqrt((v * v).mean(dim=1, keepdim=True) + 1e-6) * bits(nw)[None, :])
+
+        res = bits(x_bits)
+        for lay in self.layers:
+            qkv = lin(lay["qkv"], rms(res, lay["n1"]))
+            res = bf(res + lin(lay["o"], qkv[:, :H].contiguous()))
+            gu = lin(lay["gu"], rms(res, lay["n2"]))           # rows interleaved: gate_j, up_j
+            g, u = gu[:, 0::2], gu[:, 1::2]
+            res = bf(res + lin(lay["down"], bf(g / (1.0 + torch.exp(-g)) * u)))
+        return lin(self.lm, rms(res, self.nf))
 
     def _setup_peer(self, dev):
         """Gathered buffers in symmetric (peer-mapped) memory + flag arrays for the library's own
@@ -513,25 +588,199 @@ class Single:
         self.xq = torch.empty((m, k), dtype=torch.uint8, device="cuda")
         self.xs = torch.empty(m, dtype=torch.float32, device="cuda")
         self.bytes_per_call = linear_bytes(n, k, m, wb, n_out)
+        self.hints = os.environ.get("MC_HINTS", "1") == "1"     # each call names the next copy's weights (L2 prefetch)
+
+    def call(self, i, pdl=True):
+        """The linear on weight copy i; tells the kernel which copy comes next (L2 prefetch)."""
+        p, m, n, k = self.pkg, self.m, self.n, self.k
+        w, s = self.w[i], self.s[i]
+        if self.hints:
+            p.hint_next_weights(self.w[(i + 1) % self.copies])
+        if self.kind == 1:
+            p.launch_gate_up_swiglu(w, s, self.x, self.y, m, n, k, pdl=pdl)
+        elif self.kind == 2 and m <= 8:
+            p.launch_lm_head_argmax(w, s, self.x, self.y, n, m, n, k, 0, self.stage, self.tok, None, pdl=pdl)
+        elif self.fp8 and self.w8a8 and m > 1:
+            # the reference's batched e4m3 path: per-row activation quantiser + W8A8 GEMM (tcgen05 kind::f8f6f4)
+            p.gemm_fp8(None, self.ws, self.ws_bytes, m, n, k, w, s, self.x, self.y, self.xq, self.xs)
+        elif self.fp8:
+            (p.launch_gemv_fp8(w, s, self.x, self.y, n, k, pdl=pdl) if m == 1
+             else p.launch_gemv_fp8_rows_m(w, s, self.x, self.y, m, n, k, pdl=pdl))
+        else:
+            (p.launch_decode_gemv(w, self.x, self.y, n, k, pdl=pdl) if m == 1
+             else p.gemm_bf16(None, self.ws, self.ws_bytes, m, n, k, w, self.x, self.y))
 
     def step(self, pdl=True):
-        p, m, n, k = self.pkg, self.m, self.n, self.k
-        for w, s in zip(self.w, self.s):
-            if self.kind == 1:
-                p.launch_gate_up_swiglu(w, s, self.x, self.y, m, n, k, pdl=pdl)
-            elif self.kind == 2 and m <= 8:
-                p.launch_lm_head_argmax(w, s, self.x, self.y, n, m, n, k, 0, self.stage, self.tok, None, pdl=pdl)
-            elif self.fp8 and self.w8a8 and m > 1:
-                # the reference's batched e4m3 path: per-row activation quantiser + W8A8 GEMM (tcgen05 kind::f8f6f4)
-                p.gemm_fp8(None, self.ws, self.ws_bytes, m, n, k, w, s, self.x, self.y, self.xq, self.xs)
-            elif self.fp8:
-                (p.launch_gemv_fp8(w, s, self.x, self.y, n, k, pdl=pdl) if m == 1
-                 else p.launch_gemv_fp8_rows_m(w, s, self.x, self.y, m, n, k, pdl=pdl))
-            else:
-                (p.launch_decode_gemv(w, self.x, self.y, n, k, pdl=pdl) if m == 1
-                 else p.gemm_bf16(None, self.ws, self.ws_bytes, m, n, k, w, self.x, self.y))
-        self.launches = self.copies * (2 if self.kind == 2 or (self.fp8 and self.w8a8 and m > 1) else 1)
+        for i in range(self.copies):
+            self.call(i, pdl)
+        self.launches = self.copies * (2 if self.kind == 2 or (self.fp8 and self.w8a8 and self.m > 1) else 1)
         return self.tok
+
+    def check(self, torch):
+        """One call on copy 0 against a plain fp32 PyTorch statement of the same linear (relative L2 error
+        and largest relative error over elements that are not tiny); returns the figures, raises on a miss."""
+        self.call(0, pdl=False)
+        torch.cuda.synchronize()
+        x = self.x.view(torch.bfloat16).to(torch.float32)
+        if self.fp8:
+            ref = (x @ self.w[0].view(torch.float8_e4m3fn).to(torch.float32).T) * self.s[0][None, :]
+        else:
+            ref = x @ self.w[0].view(torch.bfloat16).to(torch.float32).T
+        if self.kind == 1:
+            rb = ref.to(torch.bfloat16).to(torch.float32)
+            g, u = rb[:, 0::2], rb[:, 1::2]
+            ref = g / (1.0 + torch.exp(-g)) * u
+        got = self.y.view(torch.bfloat16).to(torch.float32)
+        d = (got - ref).double()
+        rel = float(torch.sqrt((d * d).sum() / (ref.double() ** 2).sum()))
+        rms = float(torch.sqrt((ref.double() ** 2).mean()))
+        big = ref.abs() >= rms * 2.0 ** -7
+        # half a bf16 unit of rounding on either side is 2^-8; a SwiGLU output carries its inputs' rounding too
+        max_rel = float((d.abs()[big] / ref.abs().double()[big]).max())
+        tol = 2e-2 if self.kind == 1 else 1e-2
+        if not (rel <= 1e-2 and max_rel <= tol):
+            raise SystemExit(f"bench: {self.name} {'fp8' if self.fp8 else 'bf16'} M={self.m} differs from the fp32 statement: "
+                             f"relL2={rel:.3e} max_rel={max_rel:.3e}")
+        if self.kind == 2 and self.m <= 8:
+            want = got.argmax(dim=1).to(torch.int32)
+            vals = got.gather(1, self.tok.long()[:, None])[:, 0]
+            if not bool(((self.tok == want) | (vals == got.max(dim=1).values)).all()):
+                raise SystemExit(f"bench: lm_head argmax M={self.m} is not the maximum of its own logits")
+        return {"rel_l2": rel, "max_rel": max_rel}
+
+
+def apply_prefetch_env(pkg):
+    """MC_PREFETCH="mode[,chunk[,evict_first[,cap_mb]]]" overrides the library's L2-prefetch defaults (A/B runs)."""
+    v = os.environ.get("MC_PREFETCH")
+    if not v:
+        return "default"
+    f = [int(x) for x in v.split(",")] + [-1, -1, 0]
+    pkg.debug_set_prefetch(mode=f[0], chunk_bytes=f[1], evict_first=f[2], cap_bytes=(f[3] << 20) if f[3] > 0 else 0)
+    return v
+
+
+def time_graph(torch, stream, st, steps, warmup, use_graph=True, barrier=lambda: None):
+    """Captures one step of `st`, replays it warmup + steps times; returns (ms for `steps` steps, launch mode, run)."""
+    graph, mode = None, "eager+pdl"
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                st.step()
+            mode = "cuda-graph+pdl"
+        except Exception as e:                      # capture not possible: same kernels, eager launches
+            graph, mode = None, f"eager+pdl (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+    run = (lambda: graph.replay()) if graph is not None else (lambda: st.step())
+    barrier()
+    for _ in range(max(warmup, 3)):
+        run()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.time()
+    ev0.record(stream)
+    for _ in range(steps):
+        run()
+    ev1.record(stream)
+    barrier()
+    return ev0.elapsed_time(ev1), mode, run, (t0, time.time())
+
+
+# DRAM bytes per launch over algorithmic bytes, from the ncu captures summarised under profiles/ (read + write,
+# one launch, cold L2).  A shape without a capture reports "modelled" with the family's ratio.
+TRAFFIC = {
+    # (kernel family, workload, dtype): (ratio, source)
+}
+
+
+def traffic_for(kernel, workload, dtype, algorithmic_bytes):
+    hit = TRAFFIC.get((kernel, workload, dtype))
+    if hit is not None:
+        return algorithmic_bytes * hit[0], f"ncu dram__bytes_read.sum + dram__bytes_write.sum, {hit[1]}"
+    return None, "no ncu capture of this kernel and shape"
+
+
+def kernel_name(workload, dtype, m):
+    if m == 1:
+        return "gemv_fast_kernel"
+    if dtype == "fp8" and m <= 4:
+        return "gemv_rows_kernel"
+    return "skinny_gemm_kernel"
+
+
+def run_configs(pkg, torch, info, stream, peak, steps=12):
+    """The single-linear configurations: qkv bf16 M=1; gate_up + SwiGLU e4m3 M=1; down_proj bf16 and e4m3 for
+    M in {1..64}; lm_head bf16 M in {1, 8}.  Each entry: us per call, GB/s, fraction of the measured copy peak
+    and of 8 TB/s, kernel, and the parity of one call against the fp32 PyTorch statement."""
+    plan = [("config1", "qkv", "bf16", 1), ("config2", "gate_up", "fp8", 1)]
+    plan += [("config3", "down", d, m) for d in ("bf16", "fp8") for m in (1, 2, 4, 8, 16, 32, 64)]
+    plan += [("config4", "lm_head", "bf16", 1), ("config4", "lm_head", "bf16", 8), ("config4", "lm_head", "fp8", 1)]
+    plan += [("layer", "o", "bf16", 1), ("layer", "gate_up", "bf16", 1), ("layer", "qkv", "fp8", 1), ("layer", "o", "fp8", 1),
+             ("layer", "gate_up", "bf16", 8), ("layer", "gate_up", "fp8", 8)]
+    out = []
+    for cfg, name, dtype, m in plan:
+        sg = Single(pkg, torch, name, dtype, m, info["l2_bytes"])
+        par = sg.check(torch)
+        sg.step()
+        stream.synchronize()
+        ms, mode, run, _ = time_graph(torch, stream, sg, steps, 3)
+        us = ms * 1e3 / (steps * sg.copies)
+        gbs = sg.bytes_per_call / (us * 1e-6) / 1e9
+        kern = kernel_name(name, dtype, m)
+        traffic, src = traffic_for(kern, name, dtype, sg.bytes_per_call)
+        out.append({"config": cfg, "linear": name, "N": sg.n, "K": sg.k, "dtype": dtype, "M": m, "us_per_call": us, "GBps": gbs,
+                    "frac_of_measured": gbs / peak, "frac_of_8TBs": gbs / NOMINAL_HBM_GBS, "kernel": kern,
+                    "bytes_per_call": sg.bytes_per_call, "weight_copies": sg.copies, "launch": mode,
+                    "next_weights_hint": sg.hints, "parity_checked": "fp32 statement", "rel_l2": par["rel_l2"],
+                    "max_rel": par["max_rel"], "traffic": traffic, "traffic_source": src})
+        del sg, run
+        torch.cuda.empty_cache()
+    return out
+
+
+def check_stream(pkg, torch, st, args, world, rank, stream, tok_eager, logits_eager):
+    """What the timed graph computes, against (a) the eager step, (b) at one GPU the fp32 PyTorch statement of
+    the chain, (c) at N > 1 the one-GPU stack built on rank 0 from the same seeds.  Returns the figures."""
+    res = {}
+    if world == 1:
+        ref = st.reference_logits(st.x_in)
+        got = logits_eager.view(torch.bfloat16).to(torch.float32)
+        d = (got - ref).double()
+        rel = float(torch.sqrt((d * d).sum() / (ref.double() ** 2).sum()))
+        cos = float((got.double() * ref.double()).sum() / torch.sqrt((got.double() ** 2).sum() * (ref.double() ** 2).sum()))
+        res.update(rel_l2_vs_fp32_statement=rel, cosine=cos)
+        # 40 layers of bf16-rounded intermediates: last-bit differences upstream move the logits a little
+        if not (rel < 5e-2 and cos > 0.999):
+            raise SystemExit(f"bench: logits differ from the fp32 statement of the chain: relL2={rel:.3e} cos={cos:.6f}")
+        top2 = ref.topk(2, dim=1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 0.05
+        want = ref.argmax(dim=1).to(torch.int32)
+        if not bool(((tok_eager == want) | ~clear).all()):
+            raise SystemExit(f"bench: token {tok_eager.tolist()} differs from the fp32 statement's {want.tolist()}")
+        own = got.argmax(dim=1).to(torch.int32)
+        if not bool(((tok_eager == own) | (got.gather(1, tok_eager.long()[:, None])[:, 0] == got.max(dim=1).values)).all()):
+            raise SystemExit("bench: the token is not the maximum of the step's own logits")
+        res["tokens"] = tok_eager.tolist()
+    elif rank == 0:
+        one = Stream(pkg, torch, args.dtype, args.m, 1, 0, None)
+        one.x_in.copy_(st.x_in)
+        one.step()
+        stream.synchronize()
+        full = one.logits_view()
+        mine = full[:, st.v_lo:st.v_lo + st.v_rows]
+        same_tok = bool(torch.equal(one.tok, tok_eager))
+        if args.m == 1:
+            same = bool(torch.equal(mine, logits_eager))          # a row's arithmetic does not depend on the sharding
+        else:
+            a, b = mine.view(torch.bfloat16).float(), logits_eager.view(torch.bfloat16).float()
+            same = float(torch.sqrt(((a - b) ** 2).sum() / (a ** 2).sum())) < 1e-2
+        res.update(one_gpu_token_equal=same_tok, one_gpu_logits_shard_equal=same, tokens=tok_eager.tolist())
+        if not (same_tok and same):
+            raise SystemExit(f"bench: sharded run differs from the one-GPU stack (token equal: {same_tok}, logits shard equal: {same})")
+        pkg.stack_destroy(one.handle)
+        del one
+        torch.cuda.empty_cache()
+    return res
 
 
 def run_ours(args):
@@ -549,6 +798,7 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     info = pkg.device_check()
+    prefetch = apply_prefetch_env(pkg)
     wb = 2 if args.dtype == "bf16" else 1
     single = args.workload != "stream"
     if single and world > 1:
@@ -563,39 +813,29 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    parity = {}
     with torch.cuda.stream(stream), ClockSampler(local) as clk:
+        if single:
+            parity = st.check(torch)
         barrier()                                   # sharded kernels wait (bounded) for their peers: start together
-        st.step()                                   # eager once: sets attributes, warms NCCL
+        st.step()                                   # eager once: sets attributes
         stream.synchronize()
-        graph, mode = None, "eager+pdl"
-        if args.graph:
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    st.step()
-                mode = "cuda-graph+pdl"
-            except Exception as e:                  # capture not possible: same kernels, eager launches
-                graph, mode = None, f"eager+pdl (graph capture failed: {type(e).__name__})"
-                torch.cuda.synchronize()
-        run = (lambda: graph.replay()) if graph is not None else (lambda: st.step())
-
-        barrier()
-        for _ in range(max(args.warmup, 3)):
-            run()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        t_wall0 = time.time()
-        ev0.record(stream)
-        for _ in range(args.steps):
-            run()
-        ev1.record(stream)
-        barrier()
-        clk.window(t_wall0, time.time())
-        ms = ev0.elapsed_time(ev1)
+        if not single:
+            tok_eager = st.tok.clone()
+            logits_eager = st.logits_view().clone()
+            parity = check_stream(pkg, torch, st, args, world, rank, stream, tok_eager, logits_eager)
+        ms, mode, run, (t_wall0, t_wall1) = time_graph(torch, stream, st, args.steps, args.warmup, bool(args.graph), barrier)
+        clk.window(t_wall0, t_wall1)
+        if not single:
+            # the last timed replay computed the same step as the eager one
+            stream.synchronize()
+            if not torch.equal(st.tok, tok_eager) or not torch.equal(st.logits_view(), logits_eager):
+                raise SystemExit(f"bench: graph replay differs from the eager step (tokens {st.tok.tolist()} vs {tok_eager.tolist()})")
+            parity["graph_replay_equals_eager"] = True
         # ---- end to end: host input -> device -> linears -> result back on the host, every step
         x_dev = st.x if single else st.x_in
         res_dev = st.y if single else st.tok
-        hx = torch.randn(tuple(x_dev.shape)).to(torch.bfloat16).view(torch.int16).pin_memory()
+        hx = x_dev.cpu().pin_memory()
         hres = torch.zeros(tuple(res_dev.shape), dtype=res_dev.dtype).pin_memory()
         if not single and st.handle is not None:
             # the user-facing call: host activations in, host tokens out, one C-ABI call per step
@@ -618,11 +858,15 @@ def run_ours(args):
         e1.record(stream)
         barrier()
         ms_e2e = e0.elapsed_time(e1)
+        if not single and st.handle is not None:
+            if not torch.equal(hres, tok_eager.cpu()):
+                raise SystemExit(f"bench: the host-buffer step returned {hres.tolist()}, the eager step {tok_eager.tolist()}")
+            parity["host_step_equals_eager"] = True
 
     if getattr(st, "peer", None) is not None and int(st.peer["status"].item()) != 0:
         raise SystemExit("bench: a bounded wait of the peer all-gather kernel ran out (a rank fell behind or died)")
-    if not single and world > 1 and st.handle is not None and pkg.stack_exchange_status(st.handle, stream) != 0:
-        raise SystemExit("bench: a bounded wait of the sharded stack ran out (a rank fell behind or died)")
+    if not single and st.handle is not None and pkg.stack_exchange_status(st.handle, stream) != 0:
+        raise SystemExit("bench: a bounded wait ran out inside a kernel of the stack (a rank fell behind or died, or a pipeline stalled)")
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -637,19 +881,27 @@ def run_ours(args):
     peak, peak_kind = measured_peak()
     per_gpu = value / world
     if rank == 0:
-        cpu = cpu_reference(args.dtype, args.m, budget_s=12.0) if world == 1 and not args.no_cpu else None
+        configs = None
+        if world == 1 and not single and args.configs:
+            with torch.cuda.stream(stream):
+                configs = run_configs(pkg, torch, info, stream, peak)
+        cpu = cpu_reference(args.dtype, args.m, budget_s=10.0) if world == 1 and not args.no_cpu else None
+        kern = kernel_name(args.workload, args.dtype, args.m)
+        per_launch_bytes = (total_bytes / world) / (1 if not single else st.copies)
+        traffic, traffic_src = traffic_for(kern, args.workload, args.dtype, per_launch_bytes)
         line = {
             "metric": "decode_linear_hbm_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if wb == 2 else "fp8_e4m3_weight_only(fp32 acc)",
-            "data": "synthetic",
+            "data": "synthetic", "parity_checked": True, "parity": parity,
             "config": {"workload": workload_name(args), "launch": mode, "parallelism": f"N-sharded x{world}",
                        "gather": (None if world == 1 else
-                                  "inside the GEMV kernels: peer stores + arrival counters over NVLink (symmetric memory)" if st.handle is not None else
+                                  "inside the GEMV kernels: every output word stored to all peers over NVLink with its sequence tag (symmetric memory)" if st.handle is not None else
                                   "peer-store kernel over NVLink (symmetric memory)" if getattr(st, "peer", None) else
                                   "nccl all_gather" + (" (" + getattr(st, "peer_error", "") + ")" if getattr(st, "peer_error", "") else "")),
                        "l2": ("every call reads a different weight copy; the copies together exceed twice the L2" if single
                               else "inputs larger than L2: every step streams its own weights from HBM once"),
+                       "l2_prefetch": prefetch,
                        "bytes_per_step": total_bytes, "calls_per_step": st.launches if not single else st.copies,
                        "us_per_call": per_step_ms * 1e3 / (st.copies if single else st.launches),
                        "tokens_per_s": None if single else args.m * 1e3 / per_step_ms},
@@ -659,21 +911,20 @@ def run_ours(args):
             "clocks": clk.summary(),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_kind": f"{peak_kind} copy bandwidth", "frac_of_nominal_8TBs": per_gpu / NOMINAL_HBM_GBS,
-                         "kernel": ("gemv_fast_kernel" if args.m == 1 else "skinny_gemm_kernel" if args.m > 4 else "gemv_rows_kernel")
-                         + (" (one launch per call)" if single else " (whole step: every launch of the chain)"),
-                         # DRAM bytes per step from ncu captures of the same kernels (profiles/): read + write =
-                         # 1.0002 - 1.001 x the algorithmic bytes on every captured shape; scaled by the bytes processed
-                         "traffic": (total_bytes / world) * 1.0005 / (1 if not single else st.copies),
-                         "traffic_source": "ncu dram__bytes_read+write of gemv_fast_kernel / skinny_gemm_kernel captures, scaled"},
+                         "kernel": kern + (" (one launch per call)" if single else " (whole step: every launch of the chain)"),
+                         "traffic": traffic, "traffic_source": traffic_src},
         }
+        if configs is not None:
+            line["configs"] = configs
         if cpu is not None:
-            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample") if k in cpu}
+            for k in ("cpu_model", "numpy"):
+                if k in cpu:
+                    line["cpu_baseline"][k] = cpu[k]
         print(json.dumps(line), flush=True)
     if dist is not None:
-        # A captured graph that holds NCCL work makes the communicator teardown block on this
-        # stack: release the graph, meet once more, and leave without the teardown.
+        # leave without the communicator teardown (it can block behind captured work on this stack)
         del run
-        graph = None
         torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()
@@ -691,6 +942,7 @@ def main():
     ap.add_argument("--m", "--batch", dest="m", type=int, default=1, help="batch rows M (use --batch under torchrun, which claims --m)")
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline leg")
+    ap.add_argument("--configs", type=int, default=1, help="after the stream, measure the single-linear configurations (one GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -4,8 +4,8 @@
 // cudaStream_t and a trailing `bool pdl = false`.  An executor ported to B200 keeps its call
 // sites and includes this header instead: every function below forwards, argument for argument,
 // to the entry point of mc_sm100a_linear.h that replaces the launcher of the same name
-// (kernels.h:666-672, 721-726, 735-748, 753-764, 774-779, 785-798; GemmEngine::gemm_bf16,
-// native/runtime/gemm.h:61-63).  Status codes are the reference's mc_status_t values; the message
+// (kernels.h:666-672, 721-726, 735-748, 753-764, 774-779, 785-798; GemmEngine,
+// native/runtime/gemm.h:33-110).  Status codes are the reference's mc_status_t values; the message
 // of the last failure is mc_sm100_last_error().
 #pragma once
 
@@ -53,12 +53,41 @@ inline mc_status_t launch_post_scale_rows(uint16_t* d_y, const float* d_w_scale,
     return mc_sm100_post_scale_rows(d_y, d_w_scale, d_x_scale, M, N, (void*)stream);
 }
 
-// The slice of GemmEngine (native/runtime/gemm.h:33-110) the decode path uses: weight first.
-struct GemmEngine {
+// GemmEngine (native/runtime/gemm.h:33-110) with the same member names and operand order (weight
+// first).  The reference's engine owns a cuBLASLt handle and a plan cache; here there is no library
+// handle and no plan to search, so init / destroy / prewarm_decode_shapes keep their place in the
+// executor's start-up sequence (model.cpp, session.cpp) and have nothing to allocate: prewarm runs
+// nothing because kernel selection is a pure function of (M, N, K) with no first-call search.
+class GemmEngine {
+public:
+    GemmEngine() = default;
+    GemmEngine(const GemmEngine&) = delete;
+    GemmEngine& operator=(const GemmEngine&) = delete;
+
+    mc_status_t init() { return mc_sm100_device_check(nullptr, nullptr, nullptr, nullptr); }
+    void destroy() {}
+    mc_status_t prewarm_decode_shapes(size_t /*ws_size*/) { return MC_OK; }
+
     mc_status_t gemm_bf16(cudaStream_t stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N, uint32_t K, const void* d_w,
                           const void* d_x, void* d_y) const {
         return mc_sm100_gemm_bf16((void*)stream, d_workspace, ws_size, M, N, K, d_w, d_x, d_y);
     }
+    // W8A8: activations quantised per row into the caller's scratch, then tcgen05 kind::f8f6f4 (gemm.h:64-90)
+    mc_status_t gemm_fp8(cudaStream_t stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N, uint32_t K,
+                         const void* d_w_fp8, const float* d_w_scale, const uint16_t* d_x_bf16, uint16_t* d_y_bf16,
+                         void* d_x_fp8_scratch, float* d_x_scale_scratch) const {
+        return mc_sm100_gemm_fp8((void*)stream, d_workspace, ws_size, M, N, K, d_w_fp8, d_w_scale, d_x_bf16, d_y_bf16, d_x_fp8_scratch,
+                                 d_x_scale_scratch);
+    }
+    mc_status_t gemm_fp8_q(cudaStream_t stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N, uint32_t K,
+                           const void* d_w_fp8, const float* d_w_scale, const void* d_x_fp8, const float* d_x_scale,
+                           uint16_t* d_y_bf16) const {
+        return mc_sm100_gemm_fp8_q((void*)stream, d_workspace, ws_size, M, N, K, d_w_fp8, d_w_scale, d_x_fp8, d_x_scale, d_y_bf16);
+    }
+    // 1 = both scale vectors applied inside the kernel (the reference's preferred OUTER_VEC mode, gemm.h:92-94);
+    // the fall-back mode 2 (per-tensor scale + post-scale kernel) does not exist here.
+    int fp8_scale_mode() const { return 1; }
+    size_t cache_size() const { return 0; }
     static size_t workspace_bytes(uint32_t M, uint32_t N, uint32_t K) { return mc_sm100_gemm_workspace_bytes(M, N, K); }
 };
 

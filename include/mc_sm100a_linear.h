@@ -79,6 +79,19 @@ MC_SM100_API const char* mc_sm100_last_error(void);
 MC_SM100_API mc_status_t mc_sm100_device_check(int32_t* out_sm_count, uint64_t* out_l2_bytes,
                                   int32_t* out_cc_major, int32_t* out_cc_minor);
 
+/* Names the weights that the linear AFTER the next one will stream (any device range,
+ * 16-byte aligned).  When the L2 prefetch is switched on (mc_sm100_debug_set_prefetch; it is
+ * OFF by default) the next streaming launch made by the calling thread (GEMV, batched GEMM)
+ * asks the memory system, while it runs, to bring that range from HBM into L2
+ * (cp.async.bulk.prefetch.L2 or prefetch.global.L2).  The hint is consumed by that one launch;
+ * ranges beyond 64 MB are cut.  No counterpart in the reference; the caller that knows the
+ * chain is the executor (native/runtime/forward.cpp:206-462), and mc_sm100_stack_step names
+ * the next weights for every linear of its chain.  Measured on B200 the prefetch does not
+ * pay (the prefetched lines are mostly evicted before the next kernel reads them, and an L2
+ * hit streams only ~1.5 x faster than HBM), which is why it is off; the plumbing stays for
+ * parts where it does.  A call with NULL clears a pending hint.  Results never depend on it. */
+MC_SM100_API void mc_sm100_hint_next_weights(const void* d_next_w, uint64_t bytes);
+
 /* ---------------------------------------------------------------- M = 1 ---- */
 
 /* y[N] = bf16( W[N,K] . x[K] ), fp32 accumulate, one rounding.
@@ -330,10 +343,18 @@ MC_SM100_API mc_status_t mc_sm100_stack_step(mc_sm100_stack_t stack, const uint1
 /* Device pointer to the bf16 logits [M, vocab] the last step wrote (inside the scratch arena). */
 MC_SM100_API const uint16_t* mc_sm100_stack_logits(mc_sm100_stack_t stack);
 
+/* Device address of the stack's failure word (inside the scratch arena): 0 until a bounded wait
+ * of any kernel of a step ran out (a tensor-core pipeline that stalled, a peer rank that is gone
+ * or out of step), then 1 and sticky.  A caller that copies its results to the host anyway reads
+ * this word in the same batch of copies; mc_sm100_stack_exchange_status reads it synchronously. */
+MC_SM100_API const int32_t* mc_sm100_stack_status_word(mc_sm100_stack_t stack);
+
 /* One step on HOST buffers: H2D of x, the step (a CUDA graph captured on first use
  * per batch size when enabled and `stream` is not the default stream, else eager
- * launches of the same kernels), D2H of the tokens, one stream synchronise -- the shape
- * of mc_decode_one / mc_batch_step around a step. */
+ * launches of the same kernels), D2H of the tokens and of the failure word, one stream
+ * synchronise -- the shape of mc_decode_one / mc_batch_step around a step.  The first call
+ * for a batch size on a stream runs its step eagerly and captures the graph for the calls
+ * that follow.  MC_E_INTERNAL when the failure word is set (the tokens are then undefined). */
 MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const uint16_t* h_x, uint32_t M,
                                                   int32_t* h_tokens, void* stream);
 
@@ -351,8 +372,12 @@ MC_SM100_API mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t stack, const 
  *   mc_sm100_stack_bind_exchange(stack, addrs (host array [world], [rank] = own), stream);
  *   barrier across ranks; then every rank calls the same sequence of steps.
  * bind zeroes this rank's region.  mc_sm100_stack_exchange_status reads (and keeps) the
- * sticky failure word: 0 = every wait so far was satisfied, 1 = a wait ran out (a peer is gone
- * or out of step): the outputs of that step are undefined and the stack must be re-bound. */
+ * sticky failure word of any stack, sharded or not: 0 = every bounded wait so far was satisfied,
+ * 1 = a wait ran out (a peer is gone or out of step, or a tensor-core pipeline stalled): the
+ * outputs of that step are undefined; a sharded stack must be re-bound.
+ * The 16-bit tags of the M = 1 exchange count M = 1 steps only (batched steps keep their own
+ * counter), every tagged slot is rewritten by every M = 1 step, and the layer count is limited
+ * to 4096, so a slot can only ever hold the current or the previous tag. */
 MC_SM100_API mc_status_t mc_sm100_stack_exchange_bytes(const mc_sm100_stack_desc_t* desc, uint64_t* bytes);
 MC_SM100_API mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t stack, const uint64_t* h_peer_addrs,
                                                       uint64_t timeout_ns, void* stream);
@@ -496,6 +521,13 @@ MC_SM100_API mc_status_t mc_sm100_e4m3_from_f32_host(const float* h_in, uint64_t
  * any other value keeps the current form.  Forms 0 and 1 give identical bits;
  * form 2 sums in a different order (same contract, same tolerance). */
 MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
+
+/* A/B hook for the L2 prefetch (process-wide): mode 0 = off, 1 = bulk prefetch, 2 = one
+ * prefetch per 128-byte line; chunk_bytes = bytes per bulk instruction; evict_first != 0 marks
+ * the streaming kernels' demand loads evict-first in L2; cap_bytes = most bytes per hint.
+ * A negative value (0 for cap_bytes) keeps the current setting. */
+MC_SM100_API void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes, int32_t evict_first,
+                                              int64_t cap_bytes);
 
 /* Every wait inside the tensor-core kernel is bounded; a wait that runs out
  * makes the kernel skip its stores and raise a device-side flag.  This reads

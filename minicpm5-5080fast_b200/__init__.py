@@ -63,6 +63,7 @@ SIGNATURES = {
     "mc_sm100_stack_create": (_i32, [_vp, _vp, _vp, C.POINTER(_vp)]),
     "mc_sm100_stack_destroy": (None, [_vp]),
     "mc_sm100_stack_logits": (_vp, [_vp]),
+    "mc_sm100_stack_status_word": (_vp, [_vp]),
     "mc_sm100_stack_step": (_i32, [_vp, _vp, _u32, _vp, _vp]),
     "mc_sm100_stack_step_host": (_i32, [_vp, _vp, _u32, _vp, _vp]),
     "mc_sm100_stack_exchange_bytes": (_i32, [_vp, C.POINTER(C.c_uint64)]),
@@ -86,6 +87,25 @@ SIGNATURES = {
     "mc_sm100_wpk_writer_abort": (None, [_vp]),
     "mc_sm100_quantize_rows_host": (_i32, [_vp, _u32, _u32, _vp, _vp]),
     "mc_sm100_e4m3_from_f32_host": (_i32, [_vp, C.c_uint64, _vp]),
+    # include/mc_sm100a_runtime.h (handles are 8-byte structs passed by value: one pointer)
+    "mc_sm100_model_load": (_i32, [C.c_char_p, _vp, C.POINTER(_vp)]),
+    "mc_sm100_model_destroy": (None, [_vp]),
+    "mc_sm100_session_create": (_i32, [_vp, C.POINTER(_vp)]),
+    "mc_sm100_session_reset": (_i32, [_vp]),
+    "mc_sm100_session_destroy": (None, [_vp]),
+    "mc_sm100_prefill": (_i32, [_vp, _vp, _u32]),
+    "mc_sm100_decode_one": (_i32, [_vp, _vp, C.POINTER(_i32)]),
+    "mc_sm100_get_stats": (_i32, [_vp, _vp]),
+    "mc_sm100_batch_group_create": (_i32, [_vp, _vp, C.POINTER(_vp)]),
+    "mc_sm100_batch_group_add": (_i32, [_vp, _vp, C.POINTER(_u32)]),
+    "mc_sm100_batch_group_remove": (_i32, [_vp, _u32]),
+    "mc_sm100_batch_step": (_i32, [_vp, _vp, _u32, _vp, _vp]),
+    "mc_sm100_batch_group_destroy": (None, [_vp]),
+    "mc_sm100_debug_batch_group_stats": (_i32, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_u32), C.POINTER(_u32)]),
+    "mc_sm100_debug_model_dims": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
+    "mc_sm100_debug_session_logits": (_i32, [_vp, _vp, _u32]),
+    "mc_sm100_hint_next_weights": (None, [_vp, C.c_uint64]),
+    "mc_sm100_debug_set_prefetch": (None, [_i32, _i32, _i32, C.c_int64]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -257,6 +277,18 @@ def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=N
 
 def debug_set_math(bf16_math=-1, fp8_math=-1):
     lib().mc_sm100_debug_set_math(bf16_math, fp8_math)
+
+
+def hint_next_weights(w, nbytes=None):
+    """Names the weights the launch AFTER the next one streams (L2 prefetch); None clears the hint."""
+    if w is None:
+        lib().mc_sm100_hint_next_weights(None, 0)
+    else:
+        lib().mc_sm100_hint_next_weights(_p(w), int(nbytes if nbytes is not None else w.numel() * w.element_size()))
+
+
+def debug_set_prefetch(mode=-1, chunk_bytes=-1, evict_first=-1, cap_bytes=0):
+    lib().mc_sm100_debug_set_prefetch(mode, chunk_bytes, evict_first, cap_bytes)
 
 
 def debug_take_error() -> int:
@@ -454,3 +486,133 @@ def peer_allgather(shard, shard_bytes, slot_bytes, peer_bufs, peer_flags, my_fla
     _check(lib().mc_sm100_peer_allgather(_p(shard), shard_bytes, slot_bytes, _p(peer_bufs), _p(peer_flags),
                                          _p(my_flags), _p(epoch), rank, world, timeout_ns, _p(status),
                                          _stream(stream), int(pdl)))
+
+
+# ---- model / session / batch group (include/mc_sm100a_runtime.h) --------------------------------
+ABI_VERSION = 0x00020000
+
+
+class ModelOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("abi_version", _u32), ("device_id", _i32), ("max_sessions", _u32), ("precision", _u32),
+                ("enable_cuda_graph", _u32), ("synth_layers", _u32), ("synth_hidden", _u32), ("synth_qkv_rows", _u32),
+                ("synth_inter", _u32), ("synth_vocab", _u32), ("reserved0", _u32), ("synth_seed", C.c_uint64), ("reserved", _u32 * 4)]
+
+
+class GenerationConfig(C.Structure):
+    _fields_ = [("struct_size", _u32), ("max_new_tokens", _u32), ("temperature", C.c_float), ("top_p", C.c_float), ("top_k", _u32),
+                ("repetition_penalty", C.c_float), ("seed", C.c_uint64)]
+
+
+class RuntimeStats(C.Structure):
+    _fields_ = [("prompt_tokens", C.c_uint64), ("generated_tokens", C.c_uint64), ("prefill_us", C.c_uint64), ("decode_us", C.c_uint64),
+                ("peak_vram_bytes", C.c_uint64), ("cuda_graph_launches", C.c_uint64)]
+
+
+class BatchOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("abi_version", _u32), ("max_slots", _u32), ("max_context_tokens", _u32), ("reserved", _u32 * 4)]
+
+
+def model_options(fp8=False, max_sessions=8, graph=True, device=0, synth=None, seed=1) -> ModelOptions:
+    o = ModelOptions()
+    o.struct_size, o.abi_version, o.device_id, o.max_sessions = C.sizeof(ModelOptions), ABI_VERSION, device, max_sessions
+    o.precision, o.enable_cuda_graph, o.synth_seed = (2 if fp8 else 0), int(graph), seed
+    if synth is not None:
+        o.synth_layers, o.synth_hidden, o.synth_qkv_rows, o.synth_inter, o.synth_vocab = synth
+    return o
+
+
+def greedy_config(max_new_tokens=16) -> GenerationConfig:
+    g = GenerationConfig()
+    g.struct_size, g.max_new_tokens, g.top_k, g.repetition_penalty = C.sizeof(GenerationConfig), max_new_tokens, 1, 1.0
+    return g
+
+
+def model_load(model_dir: str, options: ModelOptions):
+    h = _vp()
+    _check(lib().mc_sm100_model_load(model_dir.encode(), C.cast(C.byref(options), _vp), C.byref(h)))
+    return h
+
+
+def model_destroy(model):
+    lib().mc_sm100_model_destroy(model)
+
+
+def model_dims(model):
+    v = [_u32() for _ in range(5)]
+    _check(lib().mc_sm100_debug_model_dims(model, *[C.byref(x) for x in v]))
+    return tuple(x.value for x in v)
+
+
+def session_create(model):
+    h = _vp()
+    _check(lib().mc_sm100_session_create(model, C.byref(h)))
+    return h
+
+
+def session_reset(session):
+    _check(lib().mc_sm100_session_reset(session))
+
+
+def session_destroy(session):
+    lib().mc_sm100_session_destroy(session)
+
+
+def prefill(session, token_ids):
+    arr = (_i32 * len(token_ids))(*token_ids)
+    _check(lib().mc_sm100_prefill(session, C.cast(arr, _vp), len(token_ids)))
+
+
+def decode_one(session, config: GenerationConfig) -> int:
+    tok = _i32(-1)
+    _check(lib().mc_sm100_decode_one(session, C.cast(C.byref(config), _vp), C.byref(tok)))
+    return tok.value
+
+
+def get_stats(session) -> RuntimeStats:
+    st = RuntimeStats()
+    _check(lib().mc_sm100_get_stats(session, C.cast(C.byref(st), _vp)))
+    return st
+
+
+def session_logits(session, count):
+    import numpy as np
+    out = np.empty(count, dtype=np.uint16)
+    _check(lib().mc_sm100_debug_session_logits(session, out.ctypes.data, count))
+    return out
+
+
+def batch_group_create(model, max_slots, max_context_tokens=0):
+    o = BatchOptions()
+    o.struct_size, o.abi_version, o.max_slots, o.max_context_tokens = C.sizeof(BatchOptions), ABI_VERSION, max_slots, max_context_tokens
+    h = _vp()
+    _check(lib().mc_sm100_batch_group_create(model, C.cast(C.byref(o), _vp), C.byref(h)))
+    return h
+
+
+def batch_group_add(group, session) -> int:
+    slot = _u32(0xFFFFFFFF)
+    _check(lib().mc_sm100_batch_group_add(group, session, C.byref(slot)))
+    return slot.value
+
+
+def batch_group_remove(group, slot):
+    _check(lib().mc_sm100_batch_group_remove(group, slot))
+
+
+def batch_step(group, slot_ids, configs):
+    n = len(slot_ids)
+    ids = (_u32 * n)(*slot_ids)
+    cfgs = (GenerationConfig * n)(*configs)
+    out = (_i32 * n)()
+    _check(lib().mc_sm100_batch_step(group, C.cast(ids, _vp), n, C.cast(cfgs, _vp), C.cast(out, _vp)))
+    return list(out)
+
+
+def batch_group_destroy(group):
+    lib().mc_sm100_batch_group_destroy(group)
+
+
+def batch_group_stats(group):
+    steps, us, members, graphs = C.c_uint64(), C.c_uint64(), _u32(), _u32()
+    _check(lib().mc_sm100_debug_batch_group_stats(group, C.byref(steps), C.byref(us), C.byref(members), C.byref(graphs)))
+    return {"steps": steps.value, "decode_us": us.value, "members": members.value, "graphs": graphs.value}

@@ -1,9 +1,11 @@
 // common.cuh -- shared device/host helpers of the sm_100a decode linear-layer library.
 #pragma once
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 
 #include <cuda_runtime.h>
 
@@ -20,6 +22,83 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Number of SMs of the current device, cached per device id (no allocation,
 // no synchronisation; cudaDeviceGetAttribute is a host-side query).
 int sm_count();
+
+// Dynamic shared memory above 48 KB has to be opted into per kernel AND per device
+// (cudaFuncSetAttribute acts on the current device).  One SmemOptIn per kernel instantiation
+// remembers what each device was raised to; host threads may race through it.
+constexpr int kMaxDevices = 64;
+struct SmemOptIn {
+    std::atomic<uint32_t> set[kMaxDevices];
+    std::mutex mu;
+    // true when `bytes` of dynamic shared memory are usable by `kern` on the current device
+    template <typename Kern>
+    cudaError_t ensure(Kern kern, size_t bytes) {
+        if (bytes <= 48u * 1024u) return cudaSuccess;
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+        if (set[dev].load(std::memory_order_acquire) >= bytes) return cudaSuccess;
+        std::lock_guard<std::mutex> lock(mu);
+        if (set[dev].load(std::memory_order_relaxed) >= bytes) return cudaSuccess;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e == cudaSuccess) set[dev].store((uint32_t)bytes, std::memory_order_release);
+        return e;
+    }
+    uint32_t recorded(int dev) const { return dev >= 0 && dev < kMaxDevices ? set[dev].load(std::memory_order_relaxed) : 0u; }
+};
+
+// ---- L2 prefetch of the NEXT linear's weights ------------------------------------
+// A decode step is a chain of dependent kernels, and a kernel can only have as many
+// weight bytes in flight before griddepcontrol.wait as its registers hold.  What hides
+// the rest of the dependent-launch latency is the 126 MB L2: while kernel i computes,
+// its CTAs ask the memory system (no registers, no completion to wait for) to bring the
+// weights of kernel i+1 from HBM into L2, so that HBM keeps streaming through the
+// bubbles between kernels and kernel i+1 reads from L2.  The caller names those weights
+// with mc_sm100_hint_next_weights(); the hint applies to the next streaming launch made
+// by the same host thread and is consumed by it.
+struct NextWeights {
+    const void* ptr;       // first byte to prefetch (16-byte aligned), nullptr = none
+    uint64_t bytes;        // multiple of 16
+};
+NextWeights take_next_weights();     // returns the pending hint of this thread and clears it
+
+// How the prefetch is issued (process-wide; a benchmark hook can change it):
+// mode 0 = off, 1 = cp.async.bulk.prefetch.L2 in chunks of `chunk` bytes per thread, 2 = one
+// prefetch.global.L2 per 128-byte line.  evict_first != 0: the demand loads of the streaming
+// kernels mark their lines evict-first in L2, so that lines already consumed leave before
+// lines prefetched for the next kernel.  cap = most bytes one hint may cover.
+struct PrefetchConfig { uint32_t mode, chunk, evict_first; uint64_t cap; };
+PrefetchConfig prefetch_config();
+
+// Device word that bounded waits of launches made by this host thread also raise when they run
+// out (besides their own flags); nullptr = none.  The decode stack points it at its failure word
+// for the duration of a step, so that one status read after the step covers every kernel.
+void set_wait_status_sink(int32_t* d_status);
+int32_t* wait_status_sink();
+
+// Kernel-side form: [ptr, ptr + bytes) cut into `per_cta` byte slices, one per CTA.
+struct PrefetchArgs {
+    const uint8_t* ptr;
+    uint64_t bytes;
+    uint32_t per_cta;      // multiple of 128
+    uint32_t chunk;        // bytes per bulk prefetch instruction, multiple of 128 (mode 1)
+    uint32_t mode;         // 0 off, 1 bulk, 2 per line
+    uint32_t evict_first;  // demand loads carry the evict-first policy
+};
+inline PrefetchArgs make_prefetch_args(const NextWeights& nw, uint32_t ctas) {
+    PrefetchArgs p{};
+    const PrefetchConfig c = prefetch_config();
+    p.evict_first = c.evict_first;
+    if (nw.ptr == nullptr || nw.bytes == 0 || c.mode == 0 || ctas == 0) return p;
+    uint64_t bytes = nw.bytes < c.cap ? nw.bytes : c.cap;
+    bytes &= ~(uint64_t)15u;
+    const uint64_t per = (((bytes + ctas - 1) / ctas) + 127u) & ~(uint64_t)127u;
+    if (per == 0 || per > 0xFFFFFF80ull) return p;
+    p.ptr = static_cast<const uint8_t*>(nw.ptr); p.bytes = bytes; p.per_cta = (uint32_t)per;
+    p.chunk = c.chunk; p.mode = c.mode;
+    return p;
+}
 
 // Launch with or without the programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>
@@ -116,6 +195,41 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+
+// The same with an L2 eviction policy (see l2_policy_stream).
+__device__ __forceinline__ uint4 ld_stream16_hint(const void* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+// evict-first: a line read once by a streaming kernel should leave L2 before lines that were
+// prefetched for the next kernel and have not been read yet.
+__device__ __forceinline__ uint64_t l2_policy_stream(bool evict_first) {
+    uint64_t first, normal;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(first));
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(normal));
+    return evict_first ? first : normal;
+}
+
+// This CTA's slice of the next kernel's weights -> L2 (no registers held, nothing to wait for).
+// Bulk form: the address is 16-byte aligned and every size a multiple of 16.
+__device__ __forceinline__ void prefetch_next_weights(const PrefetchArgs& p, uint32_t cta, uint32_t tid, uint32_t nthreads) {
+    if (p.mode == 0u) return;
+    const uint64_t lo = (uint64_t)p.per_cta * cta;
+    if (lo >= p.bytes) return;
+    const uint64_t hi = lo + p.per_cta < p.bytes ? lo + p.per_cta : p.bytes;
+    if (p.mode == 1u) {
+        for (uint64_t o = lo + (uint64_t)tid * p.chunk; o < hi; o += (uint64_t)nthreads * p.chunk) {
+            const uint32_t n = (uint32_t)(hi - o < p.chunk ? hi - o : p.chunk);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ptr + o), "r"(n) : "memory");
+        }
+    } else {
+        for (uint64_t o = lo + (uint64_t)tid * 128u; o < hi; o += (uint64_t)nthreads * 128u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.ptr + o));
+    }
 }
 
 // ---- bf16 helpers on raw bits ----

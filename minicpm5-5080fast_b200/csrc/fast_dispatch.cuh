@@ -14,24 +14,23 @@ template <int WB, int R, int U, bool PRE, bool DB, int PRO, int EPI, int T, int 
 inline mc_status_t launch_fast_one(const RowsArgs& a, cudaStream_t stream, bool pdl) {
     auto kern = gemv_fast_kernel<WB, R, U, PRE, DB, PRO, EPI, T, MINB>;
     const size_t smem = (size_t)a.K * (WB == 1 ? 4u : 2u) + (PRO == PRO_RESNORM ? (size_t)a.K * 4u : 0u);
-    static size_t smem_set = 48u * 1024u;
-    if (smem > smem_set) {
-        if (smem > 200u * 1024u) {
-            set_error("gemv: activation of %zu bytes does not fit in shared memory", smem);
-            return MC_E_UNSUPPORTED;
-        }
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) {
-            set_error("gemv: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
-            return MC_E_CUDA;
-        }
-        smem_set = smem;
+    if (smem > 200u * 1024u) {
+        set_error("gemv: activation of %zu bytes does not fit in shared memory", smem);
+        return MC_E_UNSUPPORTED;
+    }
+    static SmemOptIn optin;
+    const cudaError_t e = optin.ensure(kern, smem);
+    if (e != cudaSuccess) {
+        set_error("gemv: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+        return MC_E_CUDA;
     }
     const uint32_t groups = (a.N + R - 1) / R;
     uint32_t gx = (uint32_t)sm_count();
     if (groups < gx) gx = groups;
     if (EPI == EPI_ARGMAX && gx > kArgmaxCands) gx = kArgmaxCands;
-    (void)launch(kern, dim3(gx), dim3(T), smem, stream, pdl, a);
+    RowsArgs b = a;     // a.pf arrives as the raw hint (ptr, bytes); cut it into one slice per CTA
+    b.pf = make_prefetch_args(NextWeights{a.pf.ptr, a.pf.bytes}, gx);
+    (void)launch(kern, dim3(gx), dim3(T), smem, stream, pdl, b);
     MCL_CHECK_LAUNCH("gemv_fast");
     return MC_OK;
 }

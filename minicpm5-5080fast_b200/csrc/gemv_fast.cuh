@@ -174,6 +174,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
     const uint32_t per_lane = (nvec + 31u) / 32u;
     const bool one_batch = per_lane <= (uint32_t)U;   // a whole row fits one batch of loads
 
+    const uint64_t policy = l2_policy_stream(a.pf.evict_first != 0u);
     uint4 rawA[R][U];
     uint4 rawB[DB ? R : 1][DB ? U : 1];
     WideUnit<WB> wide[PRE ? R : 1][PRE ? U : 1];
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const uint32_t v = lane + 32u * (i0 + u);
-                raw[r][u] = (row < a.N && v < nvec) ? ld_stream16(wr + (size_t)v * 16u) : make_uint4(0u, 0u, 0u, 0u);
+                raw[r][u] = (row < a.N && v < nvec) ? ld_stream16_hint(wr + (size_t)v * 16u, policy) : make_uint4(0u, 0u, 0u, 0u);
             }
         }
     };
@@ -200,6 +201,8 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
                 for (int u = 0; u < U; ++u) widen(rawA[r][u], wide[r][u]);
         }
     }
+    // this kernel's first loads are out: now ask for the next kernel's weights (HBM -> L2)
+    prefetch_next_weights(a.pf, blockIdx.x, threadIdx.x, THREADS);
     pdl_trigger();
     pdl_wait();
     // sharded run: the activation (or the addend of the prologue) is a vector gathered from all

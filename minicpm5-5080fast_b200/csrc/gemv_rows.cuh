@@ -56,6 +56,9 @@ struct RowsArgs {
     int32_t index_base;
     // N-sharded exchange with peer GPUs (gemv_fast_kernel only; all zero = off)
     ShardIO sh;
+    // L2 prefetch of the next kernel's weights (all zero = off); gemv_fast_kernel also takes the
+    // eviction policy of its own loads from here
+    PrefetchArgs pf;
 };
 
 // ---- per-unit multiply-accumulate -------------------------------------------------
@@ -164,6 +167,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_rows_kernel(const RowsArgs
     uint32_t g = blockIdx.x + warp * gridDim.x;
     // Weights do not depend on the producer kernel: first batch goes out now.
     if (g < groups) issue(g, 0);
+    prefetch_next_weights(a.pf, blockIdx.y * gridDim.x + blockIdx.x, threadIdx.x, THREADS);
     pdl_trigger();
     pdl_wait();
 

@@ -25,12 +25,18 @@ peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t rows, uint32_t r
                       uint32_t* my_flags, uint32_t* epoch, uint32_t rank, uint32_t world,
                       unsigned long long limit_ns, int32_t* status) {
     __shared__ uint32_t s_epoch;
-    __shared__ int s_fail;
+    __shared__ int s_fail, s_dead;
     pdl_trigger();
     pdl_wait();
-    if (threadIdx.x == 0) { s_epoch = *epoch + 1u; s_fail = 0; }
+    // sticky failure: once a wait has run out (a peer fell behind or left) no later gather waits
+    // again -- it still pushes its slice and advances the epoch, so a replayed graph stays in step
+    if (threadIdx.x == 0) {
+        s_epoch = *epoch + 1u; s_fail = 0;
+        s_dead = (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) ? 1 : 0;
+    }
     __syncthreads();
     const uint32_t e = s_epoch;
+    const bool dead = s_dead != 0;
     const uint32_t units = rows * row_units;
     for (uint32_t p = 0; p < world; ++p) {
         uint4* dst = reinterpret_cast<uint4*>(peer_bufs[p]) + (size_t)rank * slot_units;
@@ -47,15 +53,20 @@ peer_allgather_kernel(const uint4* __restrict__ shard, uint32_t rows, uint32_t r
         // wait for rank threadIdx.x to have pushed its slice of this exchange to me
         const uint32_t* mine = my_flags + threadIdx.x;
         unsigned long long t0 = 0;
-        for (uint32_t spin = 0;; ++spin) {
+        for (uint32_t spin = 0; !dead; ++spin) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if ((int32_t)(v - e) >= 0) break;
             if ((spin & 31u) == 31u) {
+                if (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) break;   // another waiter gave up
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > limit_ns) { s_fail = 1; break; }
+                else if (now - t0 > limit_ns) {
+                    s_fail = 1;
+                    if (status != nullptr) *reinterpret_cast<volatile int32_t*>(status) = 1;
+                    break;
+                }
             }
         }
     }

@@ -31,24 +31,23 @@ template <int WB, int MATH, int M, int PRO, int EPI, int R, int U, int T, int B>
 inline mc_status_t launch_rows_one(const RowsArgs& a, uint32_t splits, cudaStream_t stream, bool pdl) {
     auto kern = gemv_rows_kernel<WB, M, R, U, PRO, EPI, MATH, T, B>;
     const size_t smem = (size_t)M * a.kseg * 2u;
-    static size_t smem_set = 48u * 1024u;  // per instantiation
-    if (smem > smem_set) {
-        if (smem > 200u * 1024u) {
-            set_error("gemv rows: activation tile of %zu bytes does not fit in shared memory", smem);
-            return MC_E_UNSUPPORTED;
-        }
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) {
-            set_error("gemv rows: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
-            return MC_E_CUDA;
-        }
-        smem_set = smem;
+    if (smem > 200u * 1024u) {
+        set_error("gemv rows: activation tile of %zu bytes does not fit in shared memory", smem);
+        return MC_E_UNSUPPORTED;
+    }
+    static SmemOptIn optin;   // per instantiation
+    const cudaError_t e = optin.ensure(kern, smem);
+    if (e != cudaSuccess) {
+        set_error("gemv rows: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+        return MC_E_CUDA;
     }
     const uint32_t groups = (a.N + R - 1) / R;
     const uint32_t resident = (uint32_t)(sm_count() * B);
     uint32_t gx = groups < resident ? groups : resident;
     if (EPI == EPI_ARGMAX && gx > kArgmaxCands) gx = kArgmaxCands;  // bounded stage buffer
-    (void)launch(kern, dim3(gx, splits), dim3(T), smem, stream, pdl, a);
+    RowsArgs b = a;     // a.pf arrives as the raw hint (ptr, bytes); cut it into one slice per CTA
+    b.pf = make_prefetch_args(NextWeights{a.pf.ptr, a.pf.bytes}, gx * splits);
+    (void)launch(kern, dim3(gx, splits), dim3(T), smem, stream, pdl, b);
     MCL_CHECK_LAUNCH("gemv_rows");
     return MC_OK;
 }

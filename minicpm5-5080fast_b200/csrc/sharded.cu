@@ -99,6 +99,8 @@ mc_status_t mc_sm100_gemv_sharded(int32_t prologue, int32_t epilogue, const void
     a.w = d_w; a.scale = d_scale; a.y = d_y; a.N = N; a.K = K; a.y_stride = outs; a.kseg = K;
     if (prologue == 1) { a.res_in = d_x; a.addend = d_addend; a.norm_w = d_norm_w; a.res_out = d_res_out; a.eps = eps; }
     else a.x = d_x;
+    const NextWeights nw = take_next_weights();
+    a.pf.ptr = static_cast<const uint8_t*>(nw.ptr); a.pf.bytes = nw.bytes;
     const int pro = prologue == 1 ? PRO_RESNORM : PRO_NONE, epi = epilogue == 1 ? EPI_SWIGLU : EPI_STORE;
     return wb == 2 ? launch_fast<2>(pro, epi, a, (cudaStream_t)stream, pdl != 0)
                    : launch_fast<1>(pro, epi, a, (cudaStream_t)stream, pdl != 0);

@@ -28,6 +28,9 @@
 
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 namespace mcl {
 
 namespace {
@@ -54,7 +57,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 // Bounded wait on a phase parity.  Returns false when the limit ran out or
 // another role already gave up (abort flag in shared memory).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
@@ -76,6 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     *abort_flag = 1;
     g_skinny_error = 1;
+    if (status != nullptr) *reinterpret_cast<volatile int32_t*>(status) = 1;
     return false;
 }
 
@@ -128,9 +132,8 @@ struct SkinnyArgs {
     uint32_t splits, kb_per_split;   // splits = cluster size along x
     uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
     uint32_t op_stages, raw_stages;  // ring depths (<= 8), chosen by the launcher from the grid size
-#ifdef MCL_TIMELINE
-    unsigned long long* tl;          // [grid][8] globaltimer stamps (development builds only)
-#endif
+    int32_t* status;        // optional device word set to 1 when a bounded wait ran out (the caller's failure word)
+    PrefetchArgs pf;        // L2 prefetch of the next kernel's weights (all zero = off)
 };
 
 // swizzled byte offset of 16-byte chunk `cc` (0..7) of tile row `row`
@@ -167,13 +170,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-#ifdef MCL_TIMELINE
-#define MCL_STAMP(i) do { if (a.tl != nullptr) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); a.tl[(size_t)blockIdx.x * 8 + (i)] = t_; } } while (0)
-#else
-#define MCL_STAMP(i) ((void)0)
-#endif
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    if (tid == 0) MCL_STAMP(0);
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = base, sB = base + OPS * G::A_OP, sRaw = sB + OPS * G::B_OP;
     const uint32_t bar0 = smem_u32(bars);
@@ -217,6 +214,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("barrier.cluster.wait;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     volatile int* abortp = &abort_flag;
+    // warps 2..9 have nothing to do yet: they ask for the next kernel's weights (HBM -> L2)
+    if (tid >= 64u) prefetch_next_weights(a.pf, blockIdx.x, tid - 64u, kThreads - 64u);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -231,15 +230,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mbar_expect_tx(bar, W_BYTES + (E4 ? 0u : G::B_OP));
                 tma_load_2d((E4 ? sRaw : sA) + it * W_BYTES, &map_w, bar, (int32_t)((kb0 + it) * BK), n0);
             }
-            MCL_STAMP(1);
             pdl_trigger();
             pdl_wait();
-            MCL_STAMP(2);
             bool ok = true;
             uint32_t itx = 0;   // next X stage to issue
             auto issue_x = [&](uint32_t it) {
                 const uint32_t s = it % OPS;
-                if (it >= OPS) ok = ok && mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp);
+                if (it >= OPS) ok = ok && mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp, a.status);
                 if (!ok) return;
                 if (E4) mbar_expect_tx(op_full(s), G::B_OP);
                 tma_load_2d(sB + s * G::B_OP, &map_x, op_full(s), (int32_t)((kb0 + it) * BK), 0);
@@ -248,7 +245,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (; itx < pre && ok; ++itx) issue_x(itx);              // X of the prefetched stages
                 for (uint32_t it = pre; it < nloc && ok; ++it) {          // steady state: W and X together
                     const uint32_t s = it % OPS;
-                    ok = mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp);
+                    ok = mbar_wait(op_empty(s), ((it / OPS) - 1u) & 1u, abortp, a.status);
                     if (!ok) break;
                     mbar_expect_tx(op_full(s), G::A_OP + G::B_OP);
                     tma_load_2d(sA + s * G::A_OP, &map_w, op_full(s), (int32_t)((kb0 + it) * BK), n0);
@@ -260,7 +257,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     if (itx < nloc && itx < itw) { issue_x(itx); ++itx; }   // X never runs ahead of its raw W
                     if (itw < nloc && ok) {
                         const uint32_t s = itw % RAWS;
-                        ok = mbar_wait(raw_empty(s), ((itw / RAWS) - 1u) & 1u, abortp);
+                        ok = mbar_wait(raw_empty(s), ((itw / RAWS) - 1u) & 1u, abortp, a.status);
                         if (!ok) break;
                         mbar_expect_tx(raw_full(s), G::A_RAW);
                         tma_load_2d(sRaw + s * G::A_RAW, &map_w, raw_full(s), (int32_t)((kb0 + itw) * BK), n0);
@@ -276,8 +273,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (uint32_t it = 0; it < nloc && ok; ++it) {
                 const uint32_t s = it % OPS;
                 const uint32_t par = (it / OPS) & 1u;
-                ok = mbar_wait(op_full(s), par, abortp);
-                if (ok && E4) ok = mbar_wait(conv_done(s), par, abortp);
+                ok = mbar_wait(op_full(s), par, abortp, a.status);
+                if (ok && E4) ok = mbar_wait(conv_done(s), par, abortp, a.status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = make_desc(sA + s * G::A_OP), db = make_desc(sB + s * G::B_OP);
@@ -288,7 +285,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mma_commit(op_empty(s));      // frees the stage once the MMAs have read it
             }
             if (ok && nloc > 0) mma_commit(accum_bar);
-            MCL_STAMP(3);
         }
     } else if constexpr (E4) {
         // ---------------------------------------------------------------- e4m3 -> bf16 widening
@@ -300,8 +296,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         bool ok = true;
         for (uint32_t it = group; it < nloc && ok; it += kConvThreads / kConvGroup) {
             const uint32_t sr = it % RAWS, so = it % OPS;
-            ok = mbar_wait(raw_full(sr), (it / RAWS) & 1u, abortp);
-            if (ok && it >= OPS) ok = mbar_wait(op_empty(so), ((it / OPS) - 1u) & 1u, abortp);
+            ok = mbar_wait(raw_full(sr), (it / RAWS) & 1u, abortp, a.status);
+            if (ok && it >= OPS) ok = mbar_wait(op_empty(so), ((it / OPS) - 1u) & 1u, abortp, a.status);
             if (!ok) break;
 #pragma unroll
             for (int i = 0; i < 512 / (int)kConvGroup; ++i) {
@@ -344,7 +340,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t part_s = base + G::bytes(OPS, E4 ? RAWS : 0);     // part[S][per_n][PITCH] fp32
     if (warp >= 2 && warp < 6) {
         const uint32_t q = warp & 3u;       // the TMEM lane quarter this warp may read
-        const bool ok = nloc > 0 && mbar_wait(accum_bar, 0u, abortp);
+        const bool ok = nloc > 0 && mbar_wait(accum_bar, 0u, abortp, a.status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t nl = q * 32u + lane, owner = nl / per_n;
         uint32_t remote;
@@ -372,10 +368,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
-    if (tid == 64) MCL_STAMP(4);
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-    if (tid == 0) MCL_STAMP(5);
     {
         const bool failed = *abortp != 0;
         const uint32_t nbase = (uint32_t)n0 + rank * per_n;          // first feature this CTA finishes
@@ -412,9 +406,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
     }
-    if (tid == 0) MCL_STAMP(6);
     __syncthreads();
-    if (tid == 0) MCL_STAMP(7);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -459,8 +451,8 @@ EncodeTiledFn encode_fn() {
 
 // Row-major [rows, K] matrix of 1- or 2-byte elements, box = [box_rows x box_k]; out-of-range
 // rows / columns read as zero (ragged N, M < Mpad, K tail).
-mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
-                     uint32_t box_k, uint32_t box_rows, bool swizzle128) {
+mc_status_t encode_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
+                       uint32_t box_k, uint32_t box_rows, bool swizzle128) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) {
         set_error("skinny_gemm: cuTensorMapEncodeTiled is not available from this driver");
@@ -481,19 +473,53 @@ mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t 
     return MC_OK;
 }
 
+// An encoded tensor map depends only on (address, shape, box): a step launched eagerly would
+// otherwise pay two driver encodes per GEMM.  Small process-wide cache, cleared when full.
+struct MapKey {
+    const void* ptr; uint32_t rows, K, elem, box_k, box_rows, swz;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && elem == o.elem && box_k == o.box_k && box_rows == o.box_rows && swz == o.swz;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = 0xCBF29CE484222325ull;
+        const uint64_t v[4] = {(uint64_t)(uintptr_t)k.ptr, ((uint64_t)k.rows << 32) | k.K, ((uint64_t)k.box_k << 32) | k.box_rows,
+                               ((uint64_t)k.elem << 32) | k.swz};
+        for (uint64_t x : v) { h ^= x; h *= 0x100000001B3ull; }
+        return (size_t)h;
+    }
+};
+constexpr size_t kMapCacheMax = 4096;
+
+mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
+                     uint32_t box_k, uint32_t box_rows, bool swizzle128) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{ptr, rows, K, elem_bytes, box_k, box_rows, swizzle128 ? 1u : 0u};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *map = it->second; return MC_OK; }
+    }
+    const mc_status_t s = encode_map(map, ptr, rows, K, elem_bytes, box_k, box_rows, swizzle128);
+    if (s != MC_OK) return s;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= kMapCacheMax) cache.clear();
+    cache.emplace(key, *map);
+    return MC_OK;
+}
+
 template <int MODE, int NPAD>
 mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
     using G = Ring<MODE, NPAD>;
     auto kern = skinny_gemm_kernel<MODE, NPAD>;
     constexpr size_t smem_max = 112u * 1024u;
-    static bool attr_done = false;
-    if (!attr_done) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
-        if (e != cudaSuccess) {
-            set_error("skinny_gemm: cannot raise shared memory to %zu: %s", smem_max, cudaGetErrorString(e));
-            return MC_E_CUDA;
-        }
-        attr_done = true;
+    static SmemOptIn optin;
+    const cudaError_t ae = optin.ensure(kern, smem_max);
+    if (ae != cudaSuccess) {
+        set_error("skinny_gemm: cannot raise shared memory to %zu: %s", smem_max, cudaGetErrorString(ae));
+        return MC_E_CUDA;
     }
     const size_t smem = (size_t)G::bytes(a.op_stages, MODE == SKINNY_W_E4M3 ? a.raw_stages : 0) + (size_t)(NPAD + 4) * kTileN * 4 + 2048;
     CUtensorMap map_w, map_x;
@@ -556,6 +582,8 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
     a.w_scale = w_scale; a.x_scale = x_scale; a.y = y;
     a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.kb_per_split = p.kb_per_split; a.swiglu = swiglu ? 1u : 0u;
     const uint32_t grid = p.tiles * p.splits;
+    a.pf = make_prefetch_args(take_next_weights(), grid);
+    a.status = wait_status_sink();
     // Ring depth: as many stages as fit in ~108 KB, i.e. half an SM's shared memory.  Measured:
     // a deeper ring that fills the SM is slower in a chain of launches, because the next
     // kernel's CTA can then no longer become resident (and prefetch its weights) while this

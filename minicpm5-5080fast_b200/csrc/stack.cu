@@ -44,7 +44,7 @@ static uint32_t world_of(const mc_sm100_stack_desc_t* d) { return d->world <= 1u
 
 static bool valid_desc(const mc_sm100_stack_desc_t* d) {
     if (d == nullptr || d->struct_size != sizeof(mc_sm100_stack_desc_t)) return false;
-    if (d->layers == 0 || d->hidden == 0 || d->qkv_rows < d->hidden || d->inter == 0 || d->vocab == 0) return false;
+    if (d->layers == 0 || d->layers > 4096u || d->hidden == 0 || d->qkv_rows < d->hidden || d->inter == 0 || d->vocab == 0) return false;
     if (d->precision != 0u && d->precision != 2u) return false;
     if (d->max_batch == 0 || d->max_batch > 64u) return false;
     const uint32_t mult = d->precision == 2u ? 16u : 8u;
@@ -52,7 +52,7 @@ static bool valid_desc(const mc_sm100_stack_desc_t* d) {
     if (d->reserved[0] != 0 || d->reserved[1] != 0) return false;
     if (d->world > 8u || (d->world > 1u && d->rank >= d->world) || (d->world <= 1u && d->rank != 0)) return false;
     if (d->world > 1u) {
-        // every rank owns at least one row of every layer linear; sharded steps are M = 1
+        // every rank owns at least one row of every layer linear
         const uint32_t w = d->world;
         if (shard_span(d->qkv_rows, w, w - 1u).rows == 0 || shard_span(d->hidden, w, w - 1u).rows == 0 ||
             shard_span(d->inter, w, w - 1u).rows == 0 || shard_span(d->vocab, w, w - 1u).rows == 0)
@@ -104,8 +104,10 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
     s.qkv = take(M * d->qkv_rows * 2); s.ctx = take(M * H * 2); s.o = take(M * H * 2);
     s.mid = take(M * (size_t)d->inter * 2); s.down = take(M * H * 2); s.logits = take(M * (size_t)d->vocab * 2);
     s.stage = take(mc_sm100_argmax_stage_bytes(d->max_batch)); s.tokens = take(M * 4); s.vals = take(M * 4);
-    s.sync = take(1024);  // sharded: words [0] step counter, [1] failure word, [2] shard token, [3] shard value, [5] gather epoch;
-                          // peer address tables (8 x u64 each) at bytes 64 pairs, 128 pair counters, 256.. batched buffers
+    s.sync = take(1024);  // words [0] count of M = 1 sharded steps + 1 (the exchange tags derive from it), [1] failure word
+                          // (bounded waits of any kernel of a step), [2] shard token, [3] shard value, [5] gather epoch,
+                          // [6] count of batched sharded steps + 1; peer address tables (8 x u64 each) at bytes 64 pairs,
+                          // 128 pair counters of M = 1 steps, 192 pair counters of batched steps, 256.. batched buffers
     s.total = off;
     return s;
 }
@@ -117,7 +119,7 @@ enum : uint32_t { XK_QKV = 0, XK_O = 1, XK_MID = 2, XK_DOWN = 3, XK_VECS = 4 };
 struct Exchange {
     size_t buf[XK_VECS];     // gathered qkv, o, mid, down (tagged words, M = 1)
     uint32_t pitch[XK_VECS]; // slot pitch in elements (the same for the batched buffers)
-    size_t pairs, pair_flags;   // [8][max_batch] x 8 bytes, 8 x uint32
+    size_t pairs, pair_flags;   // [8][max_batch] x 8 bytes; 8 x uint32 for M = 1 steps, then 8 x uint32 for batched steps
     // batched steps (M > 1): plain bf16 [max_batch, full width] activations + the gather's arrival flags
     size_t bbuf[XK_VECS], bflags;
     uint32_t width[XK_VECS];
@@ -135,7 +137,7 @@ static Exchange make_exchange(const mc_sm100_stack_desc_t* d) {
         off += align256((size_t)x.pitch[k] * W * 4u);
     }
     x.pairs = off; off += align256(8u * 8u * (size_t)d->max_batch);
-    x.pair_flags = off; off += align256(8u * 4u);
+    x.pair_flags = off; off += align256(16u * 4u);
     if (d->max_batch > 1u) {
         for (uint32_t k = 0; k < XK_VECS; ++k) { x.bbuf[k] = off; off += align256((size_t)d->max_batch * dims[k] * 2u); }
         x.bflags = off; off += align256(8u * 4u);
@@ -159,11 +161,20 @@ struct mc_sm100_stack {
     uint8_t* s;
     cudaGraphExec_t graph[65];     // per batch size, captured lazily
     cudaStream_t graph_stream[65];
+    int32_t* h_status;             // pinned host word the failure word is read into after a host step
 };
+
+// Weights of section `which` of layer `layer` as a prefetch hint for the launch that follows.
+static void hint(const mc_sm100_stack* st, uint32_t layer, uint32_t which);
 
 static const void* sec(const mc_sm100_stack* st, uint32_t layer, uint32_t which) {
     if (which < 10) return st->lay.per_layer[which] ? st->w + st->lay.layer_bytes * layer + st->lay.layer_off[which] : nullptr;
     return st->lay.top_bytes[which - 10] ? st->w + st->lay.top_off[which - 10] : nullptr;
+}
+
+static void hint(const mc_sm100_stack* st, uint32_t layer, uint32_t which) {
+    const size_t bytes = which < 10 ? st->lay.per_layer[which] : st->lay.top_bytes[which - 10];
+    mc_sm100_hint_next_weights(sec(st, layer, which), bytes);
 }
 
 // Sharded M = 1 step: the fused chain with every output exchanged inside the GEMV kernels.
@@ -206,15 +217,19 @@ static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int
         const float* no_scale = nullptr;
         auto scale = [&](uint32_t which) { return fp8 ? (const float*)sec(st, l, which) : no_scale; };
         mc_sm100_shard_io_t q = io(l == 0 ? -1 : (int)XK_DOWN, l, XK_QKV, l + 1);
+        hint(st, l, SEC_O);
         STEP(mc_sm100_gemv_sharded(1, 0, sec(st, l, SEC_QKV), scale(SEC_QKV_SCALE), res_in, l == 0 ? nullptr : gathered(XK_DOWN),
                                    n1, rb, nullptr, rows_q, H, d.eps, &q, sp, 1));
         q = io(XK_QKV, l + 1, XK_O, l + 1);
+        hint(st, l, SEC_GATE_UP);
         STEP(mc_sm100_gemv_sharded(0, 0, sec(st, l, SEC_O), scale(SEC_O_SCALE), gathered(XK_QKV), nullptr, nullptr, nullptr,
                                    nullptr, rows_h, H, d.eps, &q, sp, 1));
         q = io(XK_O, l + 1, XK_MID, l + 1);
+        hint(st, l, SEC_DOWN);
         STEP(mc_sm100_gemv_sharded(1, 1, sec(st, l, SEC_GATE_UP), scale(SEC_GATE_UP_SCALE), rb, gathered(XK_O), n2, ra, nullptr,
                                    2u * rows_i, H, d.eps, &q, sp, 1));
         q = io(XK_MID, l + 1, XK_DOWN, l + 1);
+        if (l + 1 < L) hint(st, l + 1, SEC_QKV); else hint(st, 0, SEC_LM_HEAD);
         STEP(mc_sm100_gemv_sharded(0, 0, sec(st, l, SEC_DOWN), scale(SEC_DOWN_SCALE), gathered(XK_MID), nullptr, nullptr, nullptr,
                                    nullptr, rows_h, I, d.eps, &q, sp, 1));
         res_in = ra;
@@ -222,6 +237,7 @@ static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int
     const mc_sm100_shard_io_t q = io(XK_DOWN, L, -1, 0);
     float* shard_val = reinterpret_cast<float*>(sync + 3);
     int32_t* shard_tok = reinterpret_cast<int32_t*>(sync + 2);
+    hint(st, 0, SEC_QKV);      // the next step starts with layer 0 again
     STEP(mc_sm100_lm_head_argmax_sharded(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), res_in,
                                          gathered(XK_DOWN), (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), rb, logits, sv.rows, H,
                                          d.eps, (int32_t)sv.lo, st->s + st->scr.stage, shard_tok, shard_val, &q, sp, 1));
@@ -272,15 +288,19 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
     const uint16_t* addend = nullptr;
     for (uint32_t l = 0; l < L; ++l) {
         STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps, sp, 1));
+        hint(st, l, SEC_O);
         STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, sq.rows, H));
         STEP(gather(XK_QKV, sq.rows));
         e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, full(XK_QKV), (size_t)d.qkv_rows * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
         if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+        hint(st, l, SEC_GATE_UP);
         STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, sh.rows, H));
         STEP(gather(XK_O, sh.rows));
         STEP(mc_sm100_residual_rmsnorm_rows(ra, full(XK_O), (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
+        hint(st, l, SEC_DOWN);
         STEP(mc_sm100_gate_up_swiglu(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), h, part, M, 2u * si.rows, H, sp, 1));
         STEP(gather(XK_MID, si.rows));
+        if (l + 1 < L) hint(st, l + 1, SEC_QKV); else hint(st, 0, SEC_LM_HEAD);
         STEP(linear(l, SEC_DOWN, SEC_DOWN_SCALE, full(XK_MID), sh.rows, I));
         STEP(gather(XK_DOWN, sh.rows));
         addend = full(XK_DOWN);
@@ -289,6 +309,7 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
     void* stage = st->s + st->scr.stage;
     int32_t* shard_tok = reinterpret_cast<int32_t*>(st->s + st->scr.tokens);
     float* shard_val = reinterpret_cast<float*>(st->s + st->scr.vals);
+    hint(st, 0, SEC_QKV);      // the next step starts with layer 0 again
     if (M <= 8u) {
         STEP(mc_sm100_lm_head_argmax(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, sv.rows, M, sv.rows, H,
                                      (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
@@ -299,15 +320,28 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
         STEP(mc_sm100_argmax_bf16(logits, M, sv.rows, sv.rows, (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
     }
     // per-row (value, index) of every rank -> tokens; the winning values land in the (otherwise unused) o scratch
-    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, M, reinterpret_cast<const uint64_t*>(sync + 16), reinterpret_cast<const uint64_t*>(sync + 32),
-                              reinterpret_cast<const uint64_t*>(own + x.pairs), reinterpret_cast<const uint32_t*>(own + x.pair_flags), sync, R, W,
+    // its own step word and arrival counters: the M = 1 exchange tags count M = 1 steps only, so a
+    // run of batched steps can never bring a stale tag back into range
+    STEP(mc_sm100_peer_argmax(shard_val, shard_tok, M, reinterpret_cast<const uint64_t*>(sync + 16), reinterpret_cast<const uint64_t*>(sync + 48),
+                              reinterpret_cast<const uint64_t*>(own + x.pairs), reinterpret_cast<const uint32_t*>(own + x.pair_flags + 32u), sync + 6, R, W,
                               st->timeout_ns, status, d_tokens, reinterpret_cast<float*>(st->s + st->scr.o), sp, 1));
 #undef STEP
     return MC_OK;
 }
 
-// One step for M rows; every launch goes to `stream`, nothing synchronises.
+static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, cudaStream_t stream);
+
+// One step for M rows; every launch goes to `stream`, nothing synchronises.  For its duration the
+// bounded waits of every kernel launched from this thread report into the stack's failure word.
 static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, cudaStream_t stream) {
+    set_wait_status_sink(reinterpret_cast<int32_t*>(st->s + st->scr.sync) + 1);
+    const mc_status_t rc = run_step_inner(st, d_x, M, d_tokens, stream);
+    set_wait_status_sink(nullptr);
+    mc_sm100_hint_next_weights(nullptr, 0);     // a step that failed half way must not leave a hint behind
+    return rc;
+}
+
+static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M, int32_t* d_tokens, cudaStream_t stream) {
     const mc_sm100_stack_desc_t& d = st->desc;
     const uint32_t H = d.hidden, Q = d.qkv_rows, I = d.inter, V = d.vocab;
     const bool fp8 = d.precision == 2u;
@@ -327,16 +361,22 @@ static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M,
         const uint16_t* addend = nullptr;
         for (uint32_t l = 0; l < d.layers; ++l) {
             const uint16_t *n1 = (const uint16_t*)sec(st, l, SEC_NORM1), *n2 = (const uint16_t*)sec(st, l, SEC_NORM2);
+            // every launch is told which weights the launch after it will stream (L2 prefetch)
+            hint(st, l, SEC_O);
             if (fp8) STEP(mc_sm100_gemv_fp8_prologue((const uint8_t*)sec(st, l, SEC_QKV), (const float*)sec(st, l, SEC_QKV_SCALE), res_in, addend, n1, rb, qkv, Q, H, d.eps, sp, 1));
             else STEP(mc_sm100_gemv_rows_prologue((const uint16_t*)sec(st, l, SEC_QKV), res_in, addend, n1, rb, qkv, Q, H, d.eps, sp, 1));
+            hint(st, l, SEC_GATE_UP);
             if (fp8) STEP(mc_sm100_gemv_fp8((const uint8_t*)sec(st, l, SEC_O), (const float*)sec(st, l, SEC_O_SCALE), qkv, o, H, H, sp, 1));
             else STEP(mc_sm100_decode_gemv((const uint16_t*)sec(st, l, SEC_O), qkv, o, H, H, MC_GEMV_TACTIC_ROWS, 0, nullptr, sp, 1));
+            hint(st, l, SEC_DOWN);
             STEP(mc_sm100_gate_up_swiglu_prologue(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), rb, o, n2, ra, mid, 2 * I, H, d.eps, sp, 1));
+            if (l + 1 < d.layers) hint(st, l + 1, SEC_QKV); else hint(st, 0, SEC_LM_HEAD);
             if (fp8) STEP(mc_sm100_gemv_fp8((const uint8_t*)sec(st, l, SEC_DOWN), (const float*)sec(st, l, SEC_DOWN_SCALE), mid, dn, H, I, sp, 1));
             else STEP(mc_sm100_decode_gemv((const uint16_t*)sec(st, l, SEC_DOWN), mid, dn, H, I, MC_GEMV_TACTIC_ROWS, 0, nullptr, sp, 1));
             res_in = ra;
             addend = dn;
         }
+        hint(st, 0, SEC_QKV);      // the next step starts with layer 0 again
         STEP(mc_sm100_lm_head_argmax_prologue(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), res_in, addend,
                                               (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), rb, logits, V, H, d.eps, 0, stage,
                                               d_tokens, vals, sp, 1));
@@ -352,16 +392,21 @@ static mc_status_t run_step(mc_sm100_stack* st, const uint16_t* d_x, uint32_t M,
     const uint16_t* addend = nullptr;
     for (uint32_t l = 0; l < d.layers; ++l) {
         STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps, sp, 1));
+        hint(st, l, SEC_O);
         STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, qkv, Q, H));
         e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, qkv, (size_t)Q * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
         if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+        hint(st, l, SEC_GATE_UP);
         STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, o, H, H));
         STEP(mc_sm100_residual_rmsnorm_rows(ra, o, (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
+        hint(st, l, SEC_DOWN);
         STEP(mc_sm100_gate_up_swiglu(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), h, mid, M, 2 * I, H, sp, 1));
+        if (l + 1 < d.layers) hint(st, l + 1, SEC_QKV); else hint(st, 0, SEC_LM_HEAD);
         STEP(linear(l, SEC_DOWN, SEC_DOWN_SCALE, mid, dn, H, I));
         addend = dn;
     }
     STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), h, M, H, d.eps, sp, 1));
+    hint(st, 0, SEC_QKV);      // the next step starts with layer 0 again
     if (M <= 8) {
         STEP(mc_sm100_lm_head_argmax(sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, V, M, V, H, 0, stage, d_tokens, vals, sp, 1));
     } else {
@@ -418,6 +463,20 @@ mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_wei
     st->timeout_ns = 0;
     std::memset(st->graph, 0, sizeof(st->graph));
     std::memset(st->graph_stream, 0, sizeof(st->graph_stream));
+    st->h_status = nullptr;
+    // control words of the scratch arena: step counters 1, failure word 0 (a sharded stack sets
+    // them again, with its peer tables, when the exchange region is bound)
+    uint32_t words[256] = {0};
+    words[0] = 1u; words[6] = 1u;
+    cudaError_t e = cudaMemcpy(st->s + st->scr.sync, words, sizeof(words), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&st->h_status), 64, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        set_error("mc_sm100_stack_create: %s", cudaGetErrorString(e));
+        if (st->h_status != nullptr) cudaFreeHost(st->h_status);
+        delete st;
+        return MC_E_CUDA;
+    }
+    *st->h_status = 0;
     *out = st;
     return MC_OK;
 }
@@ -446,13 +505,15 @@ mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t st, const uint64_t* h_
         if (g != nullptr) { cudaGraphExecDestroy(g); g = nullptr; }
     const cudaStream_t s = (cudaStream_t)stream;
     uint32_t words[256] = {0};
-    words[0] = 1u;   // step counter starts at 1; [1] failure word = 0; [5] gather epoch = 0
-    uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);          // byte 64: pairs, byte 128: pair counters
+    words[0] = 1u;   // step counters start at 1; [1] failure word = 0; [5] gather epoch = 0
+    words[6] = 1u;
+    uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);          // byte 64: pairs, byte 128 / 192: pair counters (M = 1 / batched)
     uint64_t* btables = reinterpret_cast<uint64_t*>(words + 64);         // byte 256 + 64 k: batched buffer k; byte 512: gather flags
     for (uint32_t p = 0; p < W; ++p) {
         st->peer[p] = h_peer_addrs[p];
         tables[p] = h_peer_addrs[p] + st->xch.pairs;
         tables[8 + p] = h_peer_addrs[p] + st->xch.pair_flags;
+        tables[16 + p] = h_peer_addrs[p] + st->xch.pair_flags + 32u;
         if (st->desc.max_batch > 1u) {
             for (uint32_t k = 0; k < XK_VECS; ++k) btables[8u * k + p] = h_peer_addrs[p] + st->xch.bbuf[k];
             btables[8u * XK_VECS + p] = h_peer_addrs[p] + st->xch.bflags;
@@ -469,7 +530,6 @@ mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t st, const uint64_t* h_
 mc_status_t mc_sm100_stack_exchange_status(mc_sm100_stack_t st, int32_t* h_status, void* stream) {
     clear_error();
     if (st == nullptr || h_status == nullptr) { set_error("mc_sm100_stack_exchange_status: invalid args"); return MC_E_INVALID_ARGUMENT; }
-    if (st->desc.world <= 1u) { *h_status = 0; return MC_OK; }
     const cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = cudaMemcpyAsync(h_status, st->s + st->scr.sync + 4, 4, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
@@ -481,7 +541,12 @@ void mc_sm100_stack_destroy(mc_sm100_stack_t st) {
     if (st == nullptr) return;
     for (auto& g : st->graph)
         if (g != nullptr) cudaGraphExecDestroy(g);
+    if (st->h_status != nullptr) cudaFreeHost(st->h_status);
     delete st;
+}
+
+const int32_t* mc_sm100_stack_status_word(mc_sm100_stack_t st) {
+    return st == nullptr ? nullptr : reinterpret_cast<const int32_t*>(st->s + st->scr.sync) + 1;
 }
 
 const uint16_t* mc_sm100_stack_logits(mc_sm100_stack_t st) {
@@ -509,13 +574,16 @@ mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t st, const uint16_t* h_x, u
     cudaError_t e = cudaMemcpyAsync(d_x, h_x, (size_t)M * st->desc.hidden * 2, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) { set_error("stack step: H2D failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
     mc_status_t rc = MC_OK;
+    bool done = false;
     if (st->desc.enable_cuda_graph && s != nullptr) {
         if (st->graph[M] == nullptr || st->graph_stream[M] != s) {
-            // first use of this batch size on this stream: one eager step (sets kernel attributes),
-            // then capture.  A failed capture falls back to eager launches of the same kernels
+            // first use of this batch size on this stream: THIS call's step runs eagerly (it also sets
+            // the kernel attributes), then the same sequence is captured -- a capture launches nothing --
+            // for the calls that follow.  A failed capture leaves eager launches of the same kernels
             // (the reference does the same, native/runtime/session.cpp:489-499).
             rc = run_step(st, d_x, M, d_tok, s);
             if (rc != MC_OK) return rc;
+            done = true;
             cudaGraph_t g = nullptr;
             if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
                 const mc_status_t cap = run_step(st, d_x, M, d_tok, s);
@@ -530,19 +598,23 @@ mc_status_t mc_sm100_stack_step_host(mc_sm100_stack_t st, const uint16_t* h_x, u
                 (void)cudaGetLastError();
             }
         }
-        if (st->graph[M] != nullptr) {
+        if (!done && st->graph[M] != nullptr) {
             e = cudaGraphLaunch(st->graph[M], s);
             if (e != cudaSuccess) { set_error("stack step: graph launch failed: %s", cudaGetErrorString(e)); return MC_E_GRAPH; }
-        } else {
-            rc = run_step(st, d_x, M, d_tok, s);
+            done = true;
         }
-    } else {
-        rc = run_step(st, d_x, M, d_tok, s);
     }
+    if (!done) rc = run_step(st, d_x, M, d_tok, s);
     if (rc != MC_OK) return rc;
     e = cudaMemcpyAsync(h_tokens, d_tok, (size_t)M * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(st->h_status, st->s + st->scr.sync + 4, 4, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) { set_error("stack step: D2H/sync failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    if (*st->h_status != 0) {
+        set_error("stack step: a bounded wait ran out inside a kernel (a peer rank is gone or out of step, or a tensor-core "
+                  "pipeline stalled); the tokens of this step are undefined");
+        return MC_E_INTERNAL;
+    }
     return MC_OK;
 }
 

@@ -8,15 +8,19 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared():
-    txt = open(os.path.join(ROOT, "include", "mc_sm100a_linear.h")).read()
-    return sorted(set(re.findall(r"MC_SM100_API[^;(]*?\b(mc_sm100_\w+)\s*\(", txt)))
+    names = set()
+    for h in ("mc_sm100a_linear.h", "mc_sm100a_runtime.h"):
+        txt = open(os.path.join(ROOT, "include", h)).read()
+        names |= set(re.findall(r"MC_SM100_API[^;(]*?\b(mc_sm100_\w+)\s*\(", txt))
+    return sorted(names)
 
 
 def test_header_declares_entry_points():
     names = _declared()
     assert len(names) >= 20
     for must in ("mc_sm100_decode_gemv", "mc_sm100_gemv_fp8", "mc_sm100_gemv_fp8_rows_m", "mc_sm100_gemm_bf16",
-                 "mc_sm100_gate_up_swiglu", "mc_sm100_lm_head_argmax", "mc_sm100_last_error"):
+                 "mc_sm100_gate_up_swiglu", "mc_sm100_lm_head_argmax", "mc_sm100_last_error", "mc_sm100_model_load",
+                 "mc_sm100_decode_one", "mc_sm100_batch_group_create", "mc_sm100_batch_step"):
         assert must in names
 
 

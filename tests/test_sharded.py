@@ -247,7 +247,14 @@ def test_peer_allgather_rows_and_batched_argmax(pkg, g):
     # rank 1 first with a short limit: rank 0 has not delivered -> bounded wait runs out, data still lands
     pkg.peer_allgather_rows(shards[1], M, 32, width * 2, pitch * 2, tb, tf, flags[1], epochs[1], 1, 2, timeout_ns=2_000_000, status=status)
     g.sync()
-    assert status.item() == 1
+    assert status.item() == 1 and epochs[1].item() == 1
+    # sticky: with the failure word set, a second gather does not wait again (its limit is 5 s here),
+    # still delivers and still advances its epoch
+    import time
+    t0 = time.perf_counter()
+    pkg.peer_allgather_rows(shards[1], M, 32, width * 2, pitch * 2, tb, tf, flags[1], epochs[1], 1, 2, timeout_ns=5_000_000_000, status=status)
+    g.sync()
+    assert time.perf_counter() - t0 < 1.0 and status.item() == 1 and epochs[1].item() == 2
     status.zero_()
     pkg.peer_allgather_rows(shards[0], M, 48, width * 2, pitch * 2, tb, tf, flags[0], epochs[0], 0, 2, status=status)
     g.sync()

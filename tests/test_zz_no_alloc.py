@@ -30,7 +30,8 @@ def test_static_scratch_matches_caller_scratch_twice(pkg):
         pkg.launch_decode_gemv(dw, dx, y_ref, N, K, pkg.TACTIC_SPLITK, S, part)
         pkg.launch_decode_gemv_splitk_static(dw, dx, y_new, N, K, S)
         g.sync()
-        check_close(g.host_u16(y_new), g.host_u16(y_ref), what=f"static vs caller scratch N={N} K={K} S={S}")
+        # same kernels, same fixed-order merge: the two results are the same bits
+        assert np.array_equal(g.host_u16(y_new), g.host_u16(y_ref)), f"static vs caller scratch N={N} K={K} S={S}"
         check_close(g.host_u16(y_new), onp.linear_bf16(w, x), what=f"static scratch vs oracle N={N}")
 
 
