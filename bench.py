@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 decode linear-layer path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|ref_gpu]
                     [--workload stream|qkv|gate_up|down|lm_head] [--dtype bf16|fp8] [--m M]
 
 One "step" of the default workload is one pass of the full 40-layer decode
@@ -659,8 +659,9 @@ def apply_prefetch_env(pkg):
     return v
 
 
-def time_graph(torch, stream, st, steps, warmup, use_graph=True, barrier=lambda: None):
+def time_graph(torch, stream, st, steps, warmup, use_graph=True, barrier=None):
     """Captures one step of `st`, replays it warmup + steps times; returns (ms for `steps` steps, launch mode, run)."""
+    barrier = barrier or torch.cuda.synchronize
     graph, mode = None, "eager+pdl"
     if use_graph:
         try:
@@ -931,12 +932,102 @@ def run_ours(args):
         os._exit(0)
 
 
+def run_ref_gpu(args):
+    """Comparison arm on the same GPU: per shape and M, this library against (i) the reference's own GEMV kernels
+    (native/kernels/sm120/gemv.cu, gemv_fp8.cu) compiled unmodified for sm_100a and (ii) the cuBLASLt call of its
+    batched path (native/runtime/gemm.cpp:67-128), all three with the same rotation of weight copies and the same
+    graph replay.  Needs oracle/_ref/libref_gpu.so (oracle/Makefile, target ref_gpu); prints one JSON line."""
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so")
+    if not os.path.exists(so):
+        print(json.dumps({"impl": "ref_gpu", "unavailable": "oracle/_ref/libref_gpu.so has not been built (make -C oracle ref_gpu needs the reference tree)"}))
+        return
+    pkg = importlib.import_module("minicpm5-5080fast_b200")
+    pkg.lib()
+    ref = ctypes.CDLL(so)
+    vp, u32 = ctypes.c_void_p, ctypes.c_uint32
+    ref.ref_gpu_last_error.restype = ctypes.c_char_p
+    ref.ref_gpu_decode_gemv.argtypes = [vp, vp, vp, u32, u32, vp, ctypes.c_int]
+    ref.ref_gpu_gemv_fp8.argtypes = [vp, vp, vp, vp, u32, u32, vp, ctypes.c_int]
+    ref.ref_gpu_gemv_fp8_rows_m.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, ctypes.c_int]
+    ref.ref_cublaslt_gemm_bf16.argtypes = [vp, vp, ctypes.c_size_t, u32, u32, u32, vp, vp, vp]
+    torch.cuda.set_device(0)
+    info = pkg.device_check()
+    peak, _ = measured_peak()
+    stream = torch.cuda.Stream()
+    ws = torch.empty(16 << 20, dtype=torch.uint8, device="cuda")      # the reference's 16 MB GEMM workspace
+    plan = [("config1", "qkv", "bf16", 1), ("layer", "o", "bf16", 1), ("layer", "gate_up_plain", "bf16", 1), ("config2", "gate_up_plain", "fp8", 1)]
+    plan += [("config3", "down", d, m) for d in ("bf16", "fp8") for m in (1, 2, 4, 8, 16, 32, 64)]
+    plan += [("config4", "lm_head_plain", "bf16", 1), ("config4", "lm_head_plain", "bf16", 8)]
+    Single.SHAPES["gate_up_plain"] = (2 * I, H, 0)          # the reference has no SwiGLU epilogue: plain [2I] output on both sides
+    Single.SHAPES["lm_head_plain"] = (V, H, 0)
+    rows = []
+
+    class Arm:
+        def __init__(self, sg, call):
+            self.sg, self.call, self.copies = sg, call, sg.copies
+
+        def step(self):
+            for i in range(self.copies):
+                self.call(i)
+
+    with torch.cuda.stream(stream):
+        sp = stream.cuda_stream
+        for cfg, name, dtype, m in plan:
+            sg = Single(pkg, torch, name, dtype, m, info["l2_bytes"])
+            sg.hints = False
+            y_ref = torch.zeros_like(sg.y)
+            arms = {"ours": Arm(sg, lambda i: sg.call(i))}
+            if dtype == "bf16":
+                arms["cublaslt"] = Arm(sg, lambda i: _ck(ref.ref_cublaslt_gemm_bf16(sp, ws.data_ptr(), ws.numel(), m, sg.n, sg.k, sg.w[i].data_ptr(),
+                                                                                   sg.x.data_ptr(), y_ref.data_ptr()), "cublasLt"))
+                if m == 1:
+                    arms["ref_simt_sm100a"] = Arm(sg, lambda i: _ck(ref.ref_gpu_decode_gemv(sg.w[i].data_ptr(), sg.x.data_ptr(), y_ref.data_ptr(), sg.n,
+                                                                                           sg.k, sp, 1), ref.ref_gpu_last_error()))
+            elif m == 1:
+                arms["ref_simt_sm100a"] = Arm(sg, lambda i: _ck(ref.ref_gpu_gemv_fp8(sg.w[i].data_ptr(), sg.s[i].data_ptr(), sg.x.data_ptr(), y_ref.data_ptr(),
+                                                                                    sg.n, sg.k, sp, 1), ref.ref_gpu_last_error()))
+            elif m <= 8:
+                arms["ref_simt_sm100a"] = Arm(sg, lambda i: _ck(ref.ref_gpu_gemv_fp8_rows_m(sg.w[i].data_ptr(), sg.s[i].data_ptr(), sg.x.data_ptr(),
+                                                                                           y_ref.data_ptr(), m, sg.n, sg.k, sp, 1), ref.ref_gpu_last_error()))
+            entry = {"config": cfg, "linear": name.replace("_plain", ""), "N": sg.n, "K": sg.k, "dtype": dtype, "M": m,
+                     "bytes_per_call": sg.bytes_per_call, "weight_copies": sg.copies}
+            for label, arm in arms.items():
+                arm.step()
+                stream.synchronize()
+                if label != "ours":
+                    # the comparison arm computes the same linear: its last call (copy n-1) against ours on the same copy
+                    sg.call(sg.copies - 1)
+                    stream.synchronize()
+                    a, b = sg.y.view(torch.bfloat16).float(), y_ref.view(torch.bfloat16).float()
+                    entry[label + "_rel_l2_vs_ours"] = float(torch.sqrt(((a - b) ** 2).sum() / (a ** 2).sum()))
+                ms, mode, run, _ = time_graph(torch, stream, arm, 12, 3)
+                us = ms * 1e3 / (12 * sg.copies)
+                entry[label + "_us"] = us
+                entry[label + "_GBps"] = sg.bytes_per_call / (us * 1e-6) / 1e9
+                del run
+            others = [v for k, v in entry.items() if k.endswith("_us") and not k.startswith("ours")]
+            entry["ours_vs_best_other"] = min(others) / entry["ours_us"] if others else None   # > 1: this library is faster
+            rows.append(entry)
+            del sg, arms
+            torch.cuda.empty_cache()
+    print(json.dumps({"impl": "ref_gpu", "metric": "us per call, same GPU, same rotation and graph replay", "peak_GBps": peak,
+                      "arms": {"ours": "this library", "ref_simt_sm100a": "reference gemv.cu / gemv_fp8.cu compiled unmodified for sm_100a",
+                               "cublaslt": "cuBLASLt bf16 GEMM as native/runtime/gemm.cpp:67-128 sets it up (16 MB workspace, first heuristic)"},
+                      "rows": rows}), flush=True)
+
+
+def _ck(rc, what):
+    if rc != 0:
+        raise SystemExit(f"bench: comparison arm call failed ({rc}): {what}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=600)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ref_gpu"])
     ap.add_argument("--workload", default="stream", choices=["stream", "qkv", "o", "gate_up", "down", "lm_head"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"])
     ap.add_argument("--m", "--batch", dest="m", type=int, default=1, help="batch rows M (use --batch under torchrun, which claims --m)")
@@ -946,6 +1037,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "ref_gpu":
+        run_ref_gpu(args)
     else:
         run_ours(args)
 
