@@ -704,7 +704,7 @@ def traffic_for(kernel, workload, dtype, algorithmic_bytes):
 def kernel_name(workload, dtype, m):
     if m == 1:
         return "gemv_fast_kernel"
-    if dtype == "fp8" and m <= 4:
+    if dtype == "fp8" and m <= 3:
         return "gemv_rows_kernel"
     return "skinny_gemm_kernel"
 

@@ -104,6 +104,32 @@ MC_SM100_API mc_status_t mc_sm100_decode_gemv(const uint16_t* d_w, const uint16_
                                  uint32_t N, uint32_t K, int32_t tactic, uint32_t split_s,
                                  float* d_split_partial, void* stream, int32_t pdl);
 
+/* Tactic of one shape, fixed once and used for every later call (select_decode_gemv_tactics /
+ * run_decode_gemv, native/runtime/gemv_tactic.cpp:91-258; gemv_tactic.h:42-90): the row kernel
+ * is timed against split-K with S = 8, 4, 2 on the current device, on the caller's weights, and
+ * the winner is returned (a split has to be 3 % faster: its sums run in another order).  The
+ * library-GEMM candidate of the reference does not exist here.  With d_flush (>= twice the L2)
+ * the weights come from HBM in every timed call; without it they stay L2-resident as in the
+ * reference's timing loop.  Synchronises the stream; a load-time call.  d_partial needs
+ * mc_sm100_gemv_partial_floats(max N) floats (NULL: only the row kernel is timed). */
+typedef struct mc_sm100_gemv_tactic_t {
+    uint32_t struct_size;
+    int32_t  tactic;            /* MC_GEMV_TACTIC_ROWS or MC_GEMV_TACTIC_SPLITK */
+    uint32_t split_s;           /* 1 for ROWS */
+    uint32_t best_split_s;      /* fastest split tried (0: none applied) */
+    float    us_rows, us_splitk;/* median microseconds of the row kernel and of the fastest split */
+    uint32_t reserved[2];
+} mc_sm100_gemv_tactic_t;
+MC_SM100_API uint32_t mc_sm100_gemv_pick_split_s(uint32_t N, uint32_t K);   /* the reference's static rule, target = 2 CTAs per SM of this device */
+MC_SM100_API size_t mc_sm100_gemv_partial_floats(uint32_t max_n);
+MC_SM100_API mc_status_t mc_sm100_select_decode_gemv_tactic(const uint16_t* d_w, uint32_t N, uint32_t K, const uint16_t* d_x,
+                                                            uint16_t* d_y, float* d_partial, size_t partial_floats,
+                                                            void* d_flush, size_t flush_bytes, void* stream,
+                                                            mc_sm100_gemv_tactic_t* out);
+MC_SM100_API mc_status_t mc_sm100_run_decode_gemv(const mc_sm100_gemv_tactic_t* tactic, const uint16_t* d_w,
+                                                  const uint16_t* d_x, uint16_t* d_y, uint32_t N, uint32_t K,
+                                                  float* d_partial, void* stream, int32_t pdl);
+
 /* Split-K bf16 GEMV for callers that cannot allocate device memory (a frozen
  * arena, a step replayed from a graph, a plugin host without an allocator).
  * This entry point has no counterpart in the reference.  Same arithmetic and
@@ -188,7 +214,7 @@ MC_SM100_API mc_status_t mc_sm100_interleave_rows(const void* d_src, void* d_dst
 
 /* y[M,N] = bf16( scale[n] * sum_k e4m3(W[n,k]) * x[m,k] ), weight-only fp8.
  * Replaces launch_gemv_fp8_rows_m (native/kernels/sm120/kernels.h:774-779),
- * whose cap of M <= 8 becomes M <= 64.  M <= 4 runs on CUDA cores and every
+ * whose cap of M <= 8 becomes M <= 64.  M <= 3 runs on CUDA cores and every
  * output row is bit-equal to the M=1 call on that row; larger M dequantises
  * e4m3 -> bf16 (exact) on the way into shared memory and uses tcgen05 MMA. */
 MC_SM100_API mc_status_t mc_sm100_gemv_fp8_rows_m(const uint8_t* d_w, const float* d_scale,
@@ -277,6 +303,55 @@ MC_SM100_API mc_status_t mc_sm100_lm_head_argmax_prologue(
     const uint16_t* d_norm_w, uint16_t* d_res_out, uint16_t* d_logits, uint32_t N, uint32_t n,
     float eps, int32_t index_base, void* d_stage, int32_t* d_out_idx, float* d_out_val,
     void* stream, int32_t pdl);
+
+/* ------------------------------------------------------------ sampling tail --- */
+
+/* Device-side sampling parameters of one sequence: the layout of SamplingConfigDevice
+ * (native/kernels/sm120/kernels.h:91-98), read by the kernel at run time from a fixed address so
+ * that a captured step can be replayed with other values.  rep_penalty is carried for layout
+ * compatibility and not applied here (the reference applies it in two kernels of its own before
+ * the sampler, native/kernels/sm120/sampling.cu:293-324, on the session's token history, which is
+ * not part of this path). */
+typedef struct mc_sm100_sampling_config_t {
+    float    temperature;       /* <= 0: the strongest candidate is returned and the generator not consumed */
+    float    top_p;             /* (0, 1]; >= 1 keeps all k candidates */
+    uint32_t top_k;             /* clamped to [1, 128] */
+    float    rep_penalty;
+    uint32_t flags, pad;
+} mc_sm100_sampling_config_t;
+
+/* Top-k / top-p / temperature sampling over bf16 logits [n_rows, vocab] (row stride in elements):
+ * launch_sampling_pipeline (native/kernels/sm120/kernels.h:706-716; sampling.cu:253-531, 731-806)
+ * for every row of a batch in ONE launch.  The k strongest logits under the order "value
+ * descending, index ascending" (exact, ties at the threshold towards lower indices), softmax with
+ * the temperature, cut at cumulative probability top_p, renormalise, draw with the xorshift64*
+ * generator whose 64-bit state per row lives at d_rng_state (seed it with splitmix64(seed) as the
+ * reference does, native/runtime/decode_executor.cpp:476-486; the state must not be 0).  The tail's
+ * arithmetic follows the reference statement by statement.  d_cfg: [n_rows] in device memory.
+ * n_rows <= 64.  No scratch memory. */
+MC_SM100_API mc_status_t mc_sm100_sample_topk_topp(const uint16_t* d_logits, uint32_t n_rows, uint32_t vocab,
+                                                   uint32_t row_stride, const mc_sm100_sampling_config_t* d_cfg,
+                                                   uint64_t* d_rng_state, int32_t* d_out_token, void* stream,
+                                                   int32_t pdl);
+
+/* The same over vocab shards (no counterpart in the reference, which is single-GPU and samples
+ * solo sessions only, docs/EXPERIMENT_LOG.md:169): every rank finds the k strongest of ITS shard
+ * (d_logits holds `vocab` columns of the shard, index_base = global index of column 0), stores them
+ * into every rank's exchange region through peer mappings (plain 64-bit stores, then one word per
+ * (rank, row) that carries the exchange number, st.release.sys), waits -- bounded, timeout_ns, 0 =
+ * 1 s, sticky through *d_status -- for all ranks' candidates, merges them with the same total order
+ * and draws with ITS copy of the generator state: ranks that were seeded alike draw the same token.
+ * The region (mc_sm100_sampling_exchange_bytes(max_rows, world) bytes, zeroed once, same layout on
+ * every rank) is peer-mapped by the caller; d_region_peers: device array of `world` addresses as
+ * mapped in this process; d_step: two device words {1, 0} at start, advanced by the kernel (the
+ * exchange number, and the count of rows that have finished the current one).  A token of -1
+ * means the wait ran out.  No multicast; plain peer stores and loads only. */
+MC_SM100_API size_t mc_sm100_sampling_exchange_bytes(uint32_t max_rows, uint32_t world);
+MC_SM100_API mc_status_t mc_sm100_sample_topk_topp_sharded(
+    const uint16_t* d_logits, uint32_t n_rows, uint32_t vocab, uint32_t row_stride, int32_t index_base,
+    const mc_sm100_sampling_config_t* d_cfg, uint64_t* d_rng_state, int32_t* d_out_token,
+    const uint64_t* d_region_peers, const void* d_my_region, uint32_t max_rows, uint32_t* d_step,
+    uint32_t rank, uint32_t world, uint64_t timeout_ns, int32_t* d_status, void* stream, int32_t pdl);
 
 /* ------------------------------------------------- host-buffer convenience -- */
 

@@ -57,6 +57,14 @@ SIGNATURES = {
     "mc_sm100_lm_head_argmax": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _i32]),
     "mc_sm100_lm_head_argmax_prologue": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float, _i32,
                                                 _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_gemv_pick_split_s": (_u32, [_u32, _u32]),
+    "mc_sm100_gemv_partial_floats": (C.c_size_t, [_u32]),
+    "mc_sm100_select_decode_gemv_tactic": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp, C.c_size_t, _vp, _vp]),
+    "mc_sm100_run_decode_gemv": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _i32]),
+    "mc_sm100_sample_topk_topp": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _i32]),
+    "mc_sm100_sampling_exchange_bytes": (C.c_size_t, [_u32, _u32]),
+    "mc_sm100_sample_topk_topp_sharded": (_i32, [_vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _u32, _vp, _u32, _u32,
+                                                 C.c_uint64, _vp, _vp, _i32]),
     "mc_sm100_linear_host": (_i32, [_i32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "mc_sm100_stack_sizes": (_i32, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "mc_sm100_stack_section": (_i32, [_vp, _u32, _u32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
@@ -268,6 +276,40 @@ def launch_lm_head_argmax_prologue(w, scale, res_in, addend, norm_w, res_out, lo
     _check(lib().mc_sm100_lm_head_argmax_prologue(_p(w), _p(scale), _p(res_in), _p(addend), _p(norm_w),
                                                   _p(res_out), _p(logits), N, n, eps, index_base, _p(stage),
                                                   _p(out_idx), _p(out_val), _stream(stream), int(pdl)))
+
+
+class GemvTactic(C.Structure):
+    _fields_ = [("struct_size", _u32), ("tactic", _i32), ("split_s", _u32), ("best_split_s", _u32), ("us_rows", C.c_float),
+                ("us_splitk", C.c_float), ("reserved", _u32 * 2)]
+
+
+def select_decode_gemv_tactic(w, N, K, x, y, partial=None, partial_floats=0, flush=None, stream=None) -> GemvTactic:
+    t = GemvTactic()
+    _check(lib().mc_sm100_select_decode_gemv_tactic(_p(w), N, K, _p(x), _p(y), _p(partial), partial_floats, _p(flush),
+                                                    flush.numel() * flush.element_size() if flush is not None else 0,
+                                                    _stream(stream), C.cast(C.byref(t), _vp)))
+    return t
+
+
+def run_decode_gemv(tactic, w, x, y, N, K, partial=None, stream=None, pdl=False):
+    _check(lib().mc_sm100_run_decode_gemv(C.cast(C.byref(tactic), _vp), _p(w), _p(x), _p(y), N, K, _p(partial), _stream(stream), int(pdl)))
+
+
+def sample_topk_topp(logits, n_rows, vocab, row_stride, cfg, rng_state, out_token, stream=None, pdl=False):
+    """cfg: device tensor of n_rows x 6 words (temperature, top_p as f32 bits, top_k, rep_penalty, 0, 0)."""
+    _check(lib().mc_sm100_sample_topk_topp(_p(logits), n_rows, vocab, row_stride, _p(cfg), _p(rng_state), _p(out_token),
+                                           _stream(stream), int(pdl)))
+
+
+def sampling_exchange_bytes(max_rows, world) -> int:
+    return lib().mc_sm100_sampling_exchange_bytes(max_rows, world)
+
+
+def sample_topk_topp_sharded(logits, n_rows, vocab, row_stride, index_base, cfg, rng_state, out_token, region_peers, my_region,
+                             max_rows, step, rank, world, status, timeout_ns=0, stream=None, pdl=False):
+    _check(lib().mc_sm100_sample_topk_topp_sharded(_p(logits), n_rows, vocab, row_stride, index_base, _p(cfg), _p(rng_state),
+                                                   _p(out_token), _p(region_peers), _p(my_region), max_rows, _p(step), rank, world,
+                                                   timeout_ns, _p(status), _stream(stream), int(pdl)))
 
 
 def linear_host(kind, w, scale, h_x, h_y, M, N, K, x_stage, y_stage, workspace=None, ws_size=0, stream=None):

@@ -518,9 +518,10 @@ mc_status_t mc_sm100_gemv_fp8_rows_m(const uint8_t* d_w, const float* d_scale, c
         return MC_E_INVALID_ARGUMENT;
     }
     const cudaStream_t st = (cudaStream_t)stream;
-    if (M <= 4u || !skinny_shape_ok(N, K, 1)) {
-        // CUDA cores; rows beyond four are served four at a time (byte-wise
-        // path shapes only get here with M > 4 when tcgen05 cannot take them).
+    if (M <= 3u || !skinny_shape_ok(N, K, 1)) {
+        // CUDA cores up to three rows (each row then bit-equal to the M = 1 call of the same form; four rows
+        // cost 14.4 us on the down_proj shape against 11.1 us on the tensor cores); rows beyond are served
+        // four at a time (only shapes tcgen05 cannot take get here with M > 3).
         for (uint32_t m0 = 0; m0 < M; m0 += 4u) {
             const uint32_t mc = M - m0 < 4u ? M - m0 : 4u;
             const mc_status_t s = fp8_rows_any(d_w, d_scale, d_x + (size_t)m0 * K, d_y + (size_t)m0 * N, mc,

@@ -233,3 +233,67 @@ def bf16_ulp(ref_f32: np.ndarray) -> np.ndarray:
     with np.errstate(divide="ignore"):
         e = np.floor(np.log2(np.maximum(a, np.float32(2.0 ** -126))))
     return np.exp2(e - 7).astype(np.float32)
+
+
+# ---- sampling tail (native/kernels/sm120/sampling.cu:276-283, 489-531; kernels.h:108-113) -------------
+_M64 = (1 << 64) - 1
+
+
+def splitmix64(x: int) -> int:
+    """Seed -> generator state, as the host does (native/kernels/sm120/kernels.h:108-113)."""
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return x ^ (x >> 31)
+
+
+def rng_next(state: int) -> tuple[int, int]:
+    """xorshift64*: (32-bit draw, new state) (sampling.cu:276-283)."""
+    x = state
+    x ^= x >> 12
+    x = (x ^ (x << 25)) & _M64
+    x ^= x >> 27
+    return ((x * 2685821657736338717) & _M64) >> 32, x
+
+
+def sample_topk_topp(logits_u16: np.ndarray, temperature: float, top_p: float, top_k: int, rng_state: int, index_base: int = 0):
+    """One row: the k strongest logits (value descending, index ascending), temperature softmax, top-p cut,
+    renormalisation and the draw, every sum sequential in fp32 as sampling.cu:489-531 does it.  Returns
+    (token, new generator state, margin) where margin is the distance of the uniform draw from the nearest
+    decision boundary (a device exp that differs in the last bit can only change the token when it is tiny)."""
+    v = bf16_to_f32(np.asarray(logits_u16).reshape(-1))
+    k = max(1, min(int(top_k), 128))
+    order = np.lexsort((np.arange(v.size), -v.astype(np.float64)))[:k]        # value desc, index asc
+    sv = v[order].astype(np.float32)
+    hsize = min(k, v.size)
+    if not (temperature > 0) or hsize == 1:
+        return int(order[0]) + index_base, rng_state, 1.0
+    f32 = np.float32
+    mx = sv[0]
+    sum_ = f32(0)
+    e = np.empty(hsize, dtype=np.float32)
+    for i in range(hsize):
+        e[i] = np.exp(f32((sv[i] - mx) / f32(temperature)), dtype=np.float32)
+        sum_ = f32(sum_ + e[i])
+    e = (e / sum_).astype(np.float32)
+    cut = hsize
+    if top_p < 1.0:
+        cum = f32(0)
+        for i in range(hsize):
+            cum = f32(cum + e[i])
+            if cum >= f32(top_p):
+                cut = i + 1
+                break
+    kept = f32(0)
+    for i in range(cut):
+        kept = f32(kept + e[i])
+    r, state = rng_next(rng_state)
+    u = f32(r >> 8) * f32(1.0 / 16777216.0)
+    acc, pick, margin = f32(0), cut - 1, 1.0
+    for i in range(cut):
+        acc = f32(acc + f32(e[i] / kept))
+        margin = min(margin, abs(float(u) - float(acc)))
+        if u < acc:
+            pick = i
+            break
+    return int(order[pick]) + index_base, state, margin
