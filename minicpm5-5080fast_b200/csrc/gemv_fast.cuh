@@ -203,6 +203,12 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
     }
     // this kernel's first loads are out: now ask for the next kernel's weights (HBM -> L2)
     prefetch_next_weights(a.pf, blockIdx.x, threadIdx.x, THREADS);
+    // the norm weights do not depend on the producer kernel either: this thread's first chunk of them is
+    // fetched now, which takes one L2 round trip out of the post-wait path of the prologue
+    uint4 nw_first = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (PRO == PRO_RESNORM) {
+        if (threadIdx.x < K / 8u) nw_first = __ldg(reinterpret_cast<const uint4*>(a.norm_w) + threadIdx.x);
+    }
     pdl_trigger();
     pdl_wait();
     // sharded run: the activation (or the addend of the prologue) is a vector gathered from all
@@ -260,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
         const float inv = 1.0f / sqrtf(tot / (float)K + a.eps);
         for (uint32_t c = threadIdx.x; c < nchunk; c += THREADS) {   // same thread, same chunks as pass 1
             uint16_t nw[8], bits[8];
-            unpack8(reinterpret_cast<const uint4*>(a.norm_w)[c], nw);
+            unpack8(c == threadIdx.x ? nw_first : reinterpret_cast<const uint4*>(a.norm_w)[c], nw);
             const float4 r0 = reinterpret_cast<const float4*>(tmp)[2 * c], r1 = reinterpret_cast<const float4*>(tmp)[2 * c + 1];
             const float rf[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
