@@ -178,11 +178,19 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
     uint4 rawA[R][U];
     uint4 rawB[DB ? R : 1][DB ? U : 1];
     WideUnit<WB> wide[PRE ? R : 1][PRE ? U : 1];
-    auto issue = [&](auto& raw, uint32_t g, uint32_t i0) {
+    // e4m3: the rows' scales travel with the rows' first batch of weights, so that the multiply at
+    // the end of a group does not wait for a load of its own
+    float scA[R], scB[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) { scA[r] = 1.f; scB[r] = 1.f; }
+    auto issue = [&](auto& raw, float (&sc)[R], uint32_t g, uint32_t i0) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const uint32_t row = g * R + r;
             const uint8_t* wr = wbase + (size_t)row * row_bytes;
+            if constexpr (WB == 1) {
+                if (i0 == 0u && row < a.N) sc[r] = __ldg(a.scale + row);
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const uint32_t v = lane + 32u * (i0 + u);
@@ -193,7 +201,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
 
     uint32_t g = blockIdx.x + warp * gridDim.x;
     if (g < groups) {
-        issue(rawA, g, 0);
+        issue(rawA, scA, g, 0);
         if constexpr (PRE) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
@@ -321,7 +329,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
         }
     };
     // reduce, scale, store one group
-    auto finish = [&](uint32_t g, float2 (&acc_a)[R], float2 (&acc_b)[R]) {
+    auto finish = [&](uint32_t g, const float (&sc)[R], float2 (&acc_a)[R], float2 (&acc_b)[R]) {
         float tot[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -331,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
                 const uint32_t row = g * R + r;
                 if ((fallback || s != s) && row < a.N)    // warp-uniform: s is the same in every lane
                     s = fp8_row_exact(wbase + (size_t)row * row_bytes, xb, nvec, lane);
-                if (row < a.N) s *= __ldg(a.scale + row);
+                s *= sc[r];
             }
             tot[r] = s;
         }
@@ -374,18 +382,18 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
             while (g < groups) {
                 float2 acc_a[R], acc_b[R];
                 uint32_t g2 = g + gstep;
-                if (g2 < groups) issue(rawB, g2, 0);
+                if (g2 < groups) issue(rawB, scB, g2, 0);
                 zero(acc_a, acc_b);
                 if (!skip_mac) mac_batch(rawA, use_wide, 0, acc_a, acc_b);
                 use_wide = false;
-                finish(g, acc_a, acc_b);
+                finish(g, scA, acc_a, acc_b);
                 g = g2;
                 if (g >= groups) break;
                 g2 = g + gstep;
-                if (g2 < groups) issue(rawA, g2, 0);
+                if (g2 < groups) issue(rawA, scA, g2, 0);
                 zero(acc_a, acc_b);
                 if (!skip_mac) mac_batch(rawB, false, 0, acc_a, acc_b);
-                finish(g, acc_a, acc_b);
+                finish(g, scB, acc_a, acc_b);
                 g = g2;
             }
         }
@@ -395,11 +403,11 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
             float2 acc_a[R], acc_b[R];
             zero(acc_a, acc_b);
             for (uint32_t i0 = 0; i0 < per_lane; i0 += U) {
-                if (!first) issue(rawA, g, i0);
+                if (!first) issue(rawA, scA, g, i0);
                 if (!skip_mac) mac_batch(rawA, first, i0, acc_a, acc_b);
                 first = false;
             }
-            finish(g, acc_a, acc_b);
+            finish(g, scA, acc_a, acc_b);
         }
     }
 

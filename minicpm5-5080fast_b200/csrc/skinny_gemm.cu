@@ -129,7 +129,7 @@ struct SkinnyArgs {
     const float* x_scale;   // [M] (W8A8) or null
     uint16_t* y;            // [M,N] bf16 ([M,N/2] behind the SwiGLU epilogue)
     uint32_t M, N, K;
-    uint32_t splits, kb_per_split;   // splits = cluster size along x
+    uint32_t splits;        // cluster size along x = K slices per row tile
     uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
     uint32_t op_stages, raw_stages;  // ring depths (<= 8), chosen by the launcher from the grid size
     int32_t* status;        // optional device word set to 1 when a bounded wait ran out (the caller's failure word)
@@ -183,23 +183,33 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     const uint32_t tile = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
     const uint32_t nkb = (a.K + BK - 1) / BK;
-    const uint32_t kb0 = min(nkb, split * a.kb_per_split);
-    const uint32_t kb1 = min(nkb, kb0 + a.kb_per_split);
+    const uint32_t kb0 = split * nkb / a.splits, kb1 = (split + 1u) * nkb / a.splits;   // slices differ by at most one block
     const uint32_t nloc = kb1 - kb0;
     const int32_t n0 = (int32_t)(tile * kTileN);
 
+    // the successor kernel of a chain may become resident from here on (its own first loads overlap this kernel)
+    pdl_trigger();
+    // W ring: operand ring (bf16 / W8A8) or raw ring (e4m3).  X always lands in the operand ring.
+    const uint32_t WS = E4 ? RAWS : OPS;
+    constexpr uint32_t W_BYTES = E4 ? G::A_RAW : G::A_OP;
+    const uint32_t pre = nloc < WS ? nloc : WS;
     if (tid == 0) {
         abort_flag = 0;
-        for (uint32_t s = 0; s < 8; ++s) {
-            mbar_init(op_full(s), 1);
-            mbar_init(op_empty(s), 1);
-            mbar_init(conv_done(s), kConvGroup);
-            mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), kConvGroup);
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        for (uint32_t s = 0; s < OPS; ++s) { mbar_init(op_full(s), 1); mbar_init(op_empty(s), 1); }
+        if (E4) {
+            for (uint32_t s = 0; s < OPS; ++s) mbar_init(conv_done(s), kConvGroup);
+            for (uint32_t s = 0; s < RAWS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), kConvGroup); }
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        // weights depend neither on the kernel that produces x nor on anything the other warps set up:
+        // the first ring-full is asked for before the tensor memory and the cluster are ready
+        for (uint32_t it = 0; it < pre; ++it) {
+            const uint32_t bar = E4 ? raw_full(it) : op_full(it);
+            mbar_expect_tx(bar, W_BYTES + (E4 ? 0u : G::B_OP));
+            tma_load_2d((E4 ? sRaw : sA) + it * W_BYTES, &map_w, bar, (int32_t)((kb0 + it) * BK), n0);
+        }
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     }
     if (warp == 1) {
@@ -209,9 +219,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // every CTA of the cluster is running before anyone addresses a peer's shared memory
+    // every CTA of the cluster must be running before anyone addresses a peer's shared memory: arrive now,
+    // wait only in front of the epilogue's pushes (by then the barrier has long completed)
     asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
-    asm volatile("barrier.cluster.wait;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     volatile int* abortp = &abort_flag;
     // warps 2..9 have nothing to do yet: they ask for the next kernel's weights (HBM -> L2)
@@ -220,17 +230,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------------------------------------ TMA producer
-            // W ring: operand ring (bf16 / W8A8) or raw ring (e4m3).  X always lands in the operand ring.
-            const uint32_t WS = E4 ? RAWS : OPS;
-            constexpr uint32_t W_BYTES = E4 ? G::A_RAW : G::A_OP;
-            const uint32_t pre = nloc < WS ? nloc : WS;
-            // weights do not depend on the kernel that produces x: first ring-full now
-            for (uint32_t it = 0; it < pre; ++it) {
-                const uint32_t bar = E4 ? raw_full(it) : op_full(it);
-                mbar_expect_tx(bar, W_BYTES + (E4 ? 0u : G::B_OP));
-                tma_load_2d((E4 ? sRaw : sA) + it * W_BYTES, &map_w, bar, (int32_t)((kb0 + it) * BK), n0);
-            }
-            pdl_trigger();
             pdl_wait();
             bool ok = true;
             uint32_t itx = 0;   // next X stage to issue
@@ -338,6 +337,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t per_n = kTileN / S;                               // features per owner (S divides 128)
     constexpr uint32_t PITCH = NPAD + 4;                             // fp32 per feature row: 16-byte aligned pushes, spread banks
     const uint32_t part_s = base + G::bytes(OPS, E4 ? RAWS : 0);     // part[S][per_n][PITCH] fp32
+    asm volatile("barrier.cluster.wait;" ::: "memory");              // completes the arrive of the prologue
     if (warp >= 2 && warp < 6) {
         const uint32_t q = warp & 3u;       // the TMEM lane quarter this warp may read
         const bool ok = nloc > 0 && mbar_wait(accum_bar, 0u, abortp, a.status);
@@ -416,7 +416,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 // ---- host side ---------------------------------------------------------------------------
 namespace {
 
-struct Plan { uint32_t tiles, splits, kb_per_split; };
+struct Plan { uint32_t tiles, splits; };
 
 // Cluster size along K: the largest of 8/4/2/1 that keeps the grid within two CTAs per SM
 // and leaves every CTA at least two K blocks.
@@ -428,7 +428,6 @@ Plan make_plan(uint32_t N, uint32_t K, uint32_t bk) {
     uint32_t s = 8;
     while (s > 1 && (p.tiles * s > room || nkb / s < 2)) s >>= 1;
     p.splits = s;
-    p.kb_per_split = (nkb + s - 1) / s;
     return p;
 }
 
@@ -451,7 +450,7 @@ EncodeTiledFn encode_fn() {
 
 // Row-major [rows, K] matrix of 1- or 2-byte elements, box = [box_rows x box_k]; out-of-range
 // rows / columns read as zero (ragged N, M < Mpad, K tail).
-mc_status_t encode_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
+mc_status_t encode_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t pitch, uint32_t elem_bytes,
                        uint32_t box_k, uint32_t box_rows, bool swizzle128) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) {
@@ -459,7 +458,7 @@ mc_status_t encode_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_
         return MC_E_CUDA;
     }
     const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * elem_bytes};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch * elem_bytes};   // row pitch in bytes (a multiple of 16)
     const cuuint32_t box[2] = {box_k, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
@@ -476,33 +475,33 @@ mc_status_t encode_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_
 // An encoded tensor map depends only on (address, shape, box): a step launched eagerly would
 // otherwise pay two driver encodes per GEMM.  Small process-wide cache, cleared when full.
 struct MapKey {
-    const void* ptr; uint32_t rows, K, elem, box_k, box_rows, swz;
+    const void* ptr; uint32_t rows, K, pitch, elem, box_k, box_rows, swz;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && K == o.K && elem == o.elem && box_k == o.box_k && box_rows == o.box_rows && swz == o.swz;
+        return ptr == o.ptr && rows == o.rows && K == o.K && pitch == o.pitch && elem == o.elem && box_k == o.box_k && box_rows == o.box_rows && swz == o.swz;
     }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
         uint64_t h = 0xCBF29CE484222325ull;
-        const uint64_t v[4] = {(uint64_t)(uintptr_t)k.ptr, ((uint64_t)k.rows << 32) | k.K, ((uint64_t)k.box_k << 32) | k.box_rows,
-                               ((uint64_t)k.elem << 32) | k.swz};
+        const uint64_t v[5] = {(uint64_t)(uintptr_t)k.ptr, ((uint64_t)k.rows << 32) | k.K, ((uint64_t)k.box_k << 32) | k.box_rows,
+                               ((uint64_t)k.elem << 32) | k.swz, k.pitch};
         for (uint64_t x : v) { h ^= x; h *= 0x100000001B3ull; }
         return (size_t)h;
     }
 };
 constexpr size_t kMapCacheMax = 4096;
 
-mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t elem_bytes,
+mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t K, uint32_t pitch, uint32_t elem_bytes,
                      uint32_t box_k, uint32_t box_rows, bool swizzle128) {
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    const MapKey key{ptr, rows, K, elem_bytes, box_k, box_rows, swizzle128 ? 1u : 0u};
+    const MapKey key{ptr, rows, K, pitch, elem_bytes, box_k, box_rows, swizzle128 ? 1u : 0u};
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = cache.find(key);
         if (it != cache.end()) { *map = it->second; return MC_OK; }
     }
-    const mc_status_t s = encode_map(map, ptr, rows, K, elem_bytes, box_k, box_rows, swizzle128);
+    const mc_status_t s = encode_map(map, ptr, rows, K, pitch, elem_bytes, box_k, box_rows, swizzle128);
     if (s != MC_OK) return s;
     std::lock_guard<std::mutex> lock(mu);
     if (cache.size() >= kMapCacheMax) cache.clear();
@@ -511,7 +510,7 @@ mc_status_t make_map(CUtensorMap* map, const void* ptr, uint32_t rows, uint32_t 
 }
 
 template <int MODE, int NPAD>
-mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
+mc_status_t launch_one(const void* w, const void* x, uint32_t x_pitch, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
     using G = Ring<MODE, NPAD>;
     auto kern = skinny_gemm_kernel<MODE, NPAD>;
     constexpr size_t smem_max = 112u * 1024u;
@@ -525,14 +524,14 @@ mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32
     CUtensorMap map_w, map_x;
     mc_status_t s;
     if (MODE == SKINNY_W_BF16) {
-        s = make_map(&map_w, w, a.N, a.K, 2, 64, kTileN, true);
-        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 2, 64, NPAD, true);
+        s = make_map(&map_w, w, a.N, a.K, a.K, 2, 64, kTileN, true);
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, x_pitch, 2, 64, NPAD, true);
     } else if (MODE == SKINNY_W_E4M3) {
-        s = make_map(&map_w, w, a.N, a.K, 1, 64, kTileN, false);      // raw codes, widened by warps 2-9
-        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 2, 64, NPAD, true);
+        s = make_map(&map_w, w, a.N, a.K, a.K, 1, 64, kTileN, false);      // raw codes, widened by warps 2-9
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, x_pitch, 2, 64, NPAD, true);
     } else {
-        s = make_map(&map_w, w, a.N, a.K, 1, 128, kTileN, true);
-        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, 1, 128, NPAD, true);
+        s = make_map(&map_w, w, a.N, a.K, a.K, 1, 128, kTileN, true);
+        if (s == MC_OK) s = make_map(&map_x, x, a.M, a.K, x_pitch, 1, 128, NPAD, true);
     }
     if (s != MC_OK) return s;
     cudaLaunchConfig_t cfg{};
@@ -555,10 +554,10 @@ mc_status_t launch_one(const void* w, const void* x, const SkinnyArgs& a, uint32
 }
 
 template <int MODE>
-mc_status_t launch_mode(const void* w, const void* x, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
-    if (a.M <= 16) return launch_one<MODE, 16>(w, x, a, grid, stream, pdl);
-    if (a.M <= 32) return launch_one<MODE, 32>(w, x, a, grid, stream, pdl);
-    return launch_one<MODE, 64>(w, x, a, grid, stream, pdl);
+mc_status_t launch_mode(const void* w, const void* x, uint32_t x_pitch, const SkinnyArgs& a, uint32_t grid, cudaStream_t stream, bool pdl) {
+    if (a.M <= 16) return launch_one<MODE, 16>(w, x, x_pitch, a, grid, stream, pdl);
+    if (a.M <= 32) return launch_one<MODE, 32>(w, x, x_pitch, a, grid, stream, pdl);
+    return launch_one<MODE, 64>(w, x, x_pitch, a, grid, stream, pdl);
 }
 
 }  // namespace
@@ -572,15 +571,18 @@ bool skinny_shape_ok(uint32_t N, uint32_t K, int wb) {
 size_t skinny_workspace_bytes(uint32_t, uint32_t, uint32_t) { return 0; }
 
 mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uint16_t* x, const float* x_scale,
-                        uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu, cudaStream_t stream, bool pdl) {
-    if (M == 0 || M > 64 || !aligned16(w) || !aligned16(x) || (swiglu && (N & 1u))) {
-        set_error("skinny_gemm: invalid args (M=%u N=%u K=%u)", M, N, K);
+                        uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu, cudaStream_t stream, bool pdl,
+                        uint32_t x_pitch) {
+    if (x_pitch == 0u) x_pitch = K;
+    const uint32_t x_elem = mode == SKINNY_W8A8 ? 1u : 2u;
+    if (M == 0 || M > 64 || !aligned16(w) || !aligned16(x) || (swiglu && (N & 1u)) || x_pitch < K || ((x_pitch * x_elem) & 15u) != 0u) {
+        set_error("skinny_gemm: invalid args (M=%u N=%u K=%u x_pitch=%u)", M, N, K, x_pitch);
         return MC_E_INVALID_ARGUMENT;
     }
     const Plan p = make_plan(N, K, mode == SKINNY_W8A8 ? 128u : 64u);
     SkinnyArgs a{};
     a.w_scale = w_scale; a.x_scale = x_scale; a.y = y;
-    a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.kb_per_split = p.kb_per_split; a.swiglu = swiglu ? 1u : 0u;
+    a.M = M; a.N = N; a.K = K; a.splits = p.splits; a.swiglu = swiglu ? 1u : 0u;
     const uint32_t grid = p.tiles * p.splits;
     a.pf = make_prefetch_args(take_next_weights(), grid);
     a.status = wait_status_sink();
@@ -603,9 +605,9 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
         if (a.op_stages < 2u) a.op_stages = 2u;
         a.raw_stages = 1u;
     }
-    if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(w, x, a, grid, stream, pdl);
-    if (mode == SKINNY_W_E4M3) return launch_mode<SKINNY_W_E4M3>(w, x, a, grid, stream, pdl);
-    return launch_mode<SKINNY_W8A8>(w, x, a, grid, stream, pdl);
+    if (mode == SKINNY_W_BF16) return launch_mode<SKINNY_W_BF16>(w, x, x_pitch, a, grid, stream, pdl);
+    if (mode == SKINNY_W_E4M3) return launch_mode<SKINNY_W_E4M3>(w, x, x_pitch, a, grid, stream, pdl);
+    return launch_mode<SKINNY_W8A8>(w, x, x_pitch, a, grid, stream, pdl);
 }
 
 // 1 when a bounded wait of the tensor-core kernel ran out since the last call (and clears it).

@@ -13,6 +13,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "skinny_gemm.cuh"
 
 namespace mcl {
 
@@ -249,6 +250,25 @@ static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int
     return MC_OK;
 }
 
+// o_proj of a batched step: its activation is the first `hidden` columns of the [M, pitch] qkv
+// result (the stand-in for attention).  The tensor-core GEMM reads that column block in place
+// through its tensor map; the CUDA-core forms (fewest rows, shapes TMA cannot take) get a packed copy.
+static mc_status_t linear_cols(mc_sm100_stack* st, uint32_t M, uint32_t l, const uint16_t* src, uint32_t pitch, uint16_t* ctx,
+                               uint16_t* y, uint32_t rows, cudaStream_t stream) {
+    const mc_sm100_stack_desc_t& d = st->desc;
+    const bool fp8 = d.precision == 2u;
+    const uint32_t H = d.hidden;
+    const void* w = sec(st, l, SEC_O);
+    const float* sc = fp8 ? (const float*)sec(st, l, SEC_O_SCALE) : nullptr;
+    const bool tensor = (fp8 ? M >= 4u : M >= 2u) && mcl::skinny_shape_ok(rows, H, fp8 ? 1 : 2) && (pitch & 7u) == 0u;
+    if (tensor)
+        return mcl::skinny_gemm(fp8 ? mcl::SKINNY_W_E4M3 : mcl::SKINNY_W_BF16, w, sc, src, nullptr, y, M, rows, H, false, stream, true, pitch);
+    const cudaError_t e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, src, (size_t)pitch * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) { mcl::set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
+    return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)w, sc, ctx, y, M, rows, H, (void*)stream, 1)
+               : mc_sm100_gemm_bf16((void*)stream, nullptr, 0, M, rows, H, w, ctx, y);
+}
+
 // Sharded batched step (M > 1): every rank runs the batched chain on its rows of each matrix; the
 // [M, rows] result of a linear is scattered into column slot `rank` of every rank's [M, width]
 // buffer by one small kernel per linear (mc_sm100_peer_allgather_rows), which is then the activation
@@ -291,10 +311,8 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
         hint(st, l, SEC_O);
         STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, sq.rows, H));
         STEP(gather(XK_QKV, sq.rows));
-        e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, full(XK_QKV), (size_t)d.qkv_rows * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
-        if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
         hint(st, l, SEC_GATE_UP);
-        STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, sh.rows, H));
+        STEP(linear_cols(st, M, l, full(XK_QKV), x.width[XK_QKV], ctx, part, sh.rows, stream));
         STEP(gather(XK_O, sh.rows));
         STEP(mc_sm100_residual_rmsnorm_rows(ra, full(XK_O), (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
         hint(st, l, SEC_DOWN);
@@ -394,10 +412,8 @@ static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint3
         STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps, sp, 1));
         hint(st, l, SEC_O);
         STEP(linear(l, SEC_QKV, SEC_QKV_SCALE, h, qkv, Q, H));
-        e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, qkv, (size_t)Q * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
-        if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
         hint(st, l, SEC_GATE_UP);
-        STEP(linear(l, SEC_O, SEC_O_SCALE, ctx, o, H, H));
+        STEP(linear_cols(st, M, l, qkv, Q, ctx, o, H, stream));
         STEP(mc_sm100_residual_rmsnorm_rows(ra, o, (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, sp, 1));
         hint(st, l, SEC_DOWN);
         STEP(mc_sm100_gate_up_swiglu(sec(st, l, SEC_GATE_UP), (const float*)sec(st, l, SEC_GATE_UP_SCALE), h, mid, M, 2 * I, H, sp, 1));
