@@ -498,7 +498,7 @@ class Stream:
         """One GPU: the whole step through the C ABI's decode-stack object."""
         m = self.m
         self.pkg.stack_step(self.handle, self.x_in, m, self.tok)
-        self.launches = ((4 * L + 2 + (1 if self.world > 1 else 0)) if m == 1
+        self.launches = (1 if (m == 1 and self.world == 1 and CHAIN[0]) else (4 * L + 2 + (1 if self.world > 1 else 0)) if m == 1
                          else (6 * L + 1 + (2 if m <= 4 else 3) + ((4 * L + 1) if self.world > 1 else 0)))
         return self.tok
 
@@ -653,8 +653,18 @@ class Single:
         return {"rel_l2": rel, "max_rel": max_rel}
 
 
+CHAIN = [False]       # whether M = 1 steps of a one-GPU stack run as one persistent kernel (library default: no)
+
+
+def set_chain(pkg, on):
+    pkg.debug_set_chain(on)
+    CHAIN[0] = bool(on)
+
+
 def apply_prefetch_env(pkg):
     """MC_PREFETCH="mode[,chunk[,evict_first[,cap_mb]]]" overrides the library's L2-prefetch defaults (A/B runs)."""
+    if os.environ.get("MC_CHAIN") is not None:       # MC_CHAIN=0: one kernel per linear instead of the one-launch M = 1 chain
+        set_chain(pkg, os.environ["MC_CHAIN"] != "0")
     v = os.environ.get("MC_PREFETCH")
     if not v:
         return "default"
@@ -717,6 +727,8 @@ def traffic_for(kernel, workload, dtype, algorithmic_bytes):
 
 
 def kernel_name(workload, dtype, m):
+    if m == 1 and workload == "stream" and CHAIN[0]:
+        return "decode_chain_kernel"
     if m == 1:
         return "gemv_fast_kernel"
     if dtype == "fp8" and m <= 3:
@@ -751,6 +763,46 @@ def run_configs(pkg, torch, info, stream, peak, steps=12):
                     "max_rel": par["max_rel"], "traffic": traffic, "traffic_source": src})
         del sg, run
         torch.cuda.empty_cache()
+    return out
+
+
+def run_stream_configs(pkg, torch, args, stream, peak, steps=20):
+    """The other whole-step streams next to the headline: e4m3 and bf16, M = 1 and M = 8, each checked like the
+    headline before it is timed, and the M = 1 step as ONE persistent kernel (the library's alternative launch form,
+    off by default).  One entry each: ms per step, GB/s, fraction of the measured copy peak."""
+    import copy
+    plan = [("bf16", 1, False), ("fp8", 1, False), ("bf16", 8, False), ("fp8", 8, False), ("bf16", 1, True), ("fp8", 1, True)]
+    out = []
+    for dtype, m, chain in plan:
+        if (dtype, m, chain) == (args.dtype, args.m, False):
+            continue                                  # the headline itself
+        a = copy.copy(args)
+        a.dtype, a.m = dtype, m
+        set_chain(pkg, chain)
+        try:
+            st = Stream(pkg, torch, dtype, m, 1, 0, None)
+            st.step()
+            stream.synchronize()
+            tok, logits = st.tok.clone(), st.logits_view().clone()
+            par = check_stream(pkg, torch, st, a, 1, 0, stream, tok, logits)
+            ms, mode, run, _ = time_graph(torch, stream, st, steps, 3)
+            stream.synchronize()
+            if not torch.equal(st.tok, tok) or not torch.equal(st.logits_view(), logits):
+                raise SystemExit(f"bench: {dtype} M={m} stream: graph replay differs from the eager step")
+            if pkg.stack_exchange_status(st.handle, stream) != 0:
+                raise SystemExit(f"bench: {dtype} M={m} stream: a bounded wait ran out")
+            nbytes = stream_bytes(m, 2 if dtype == "bf16" else 1, 1, 0)
+            gbs = nbytes / (ms / steps * 1e-3) / 1e9
+            out.append({"config": "config5", "stream": f"40 layers + lm_head, {dtype}, M={m}", "dtype": dtype, "M": m,
+                        "launch_form": "one persistent kernel per step" if chain else "one kernel per linear",
+                        "ms_per_step": ms / steps, "GBps": gbs, "frac_of_measured": gbs / peak, "frac_of_8TBs": gbs / NOMINAL_HBM_GBS,
+                        "launch": mode, "tokens_per_s": m * 1e3 / (ms / steps), "parity_checked": "fp32 statement + graph replay",
+                        "rel_l2": par.get("rel_l2_vs_fp32_statement"), "cosine": par.get("cosine")})
+            pkg.stack_destroy(st.handle)
+            del st, run
+            torch.cuda.empty_cache()
+        finally:
+            set_chain(pkg, False)
     return out
 
 
@@ -909,6 +961,8 @@ def run_ours(args):
         if world == 1 and not single and args.configs:
             with torch.cuda.stream(stream):
                 configs = run_configs(pkg, torch, info, stream, peak)
+                if L == 40:
+                    configs += run_stream_configs(pkg, torch, args, stream, peak)
         cpu = cpu_reference(args.dtype, args.m, budget_s=10.0) if world == 1 and not args.no_cpu else None
         kern = kernel_name(args.workload, args.dtype, args.m)
         per_launch_bytes = (total_bytes / world) / (1 if not single else st.copies)

@@ -604,6 +604,13 @@ MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
 MC_SM100_API void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes, int32_t evict_first,
                                               int64_t cap_bytes);
 
+/* A/B hook (process-wide): on != 0 runs an M = 1 step of a one-GPU stack as ONE persistent kernel
+ * (every linear of every layer and the lm_head; weights streamed through a shared-memory ring that
+ * does not stop at the dependencies between linears; outputs handed from CTA to CTA as tagged words
+ * behind one arrival counter per linear); 0 (default: it measured faster) launches one kernel per
+ * linear.  Both give the same bits.  Takes effect for steps issued (and graphs captured) afterwards. */
+MC_SM100_API void mc_sm100_debug_set_chain(int32_t on);
+
 /* Every wait inside the tensor-core kernel is bounded; a wait that runs out
  * makes the kernel skip its stores and raise a device-side flag.  This reads
  * the flag (synchronising copy) and clears it: 0 = no wait ever ran out. */

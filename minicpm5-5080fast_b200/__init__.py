@@ -114,6 +114,7 @@ SIGNATURES = {
     "mc_sm100_debug_session_logits": (_i32, [_vp, _vp, _u32]),
     "mc_sm100_hint_next_weights": (None, [_vp, C.c_uint64]),
     "mc_sm100_debug_set_prefetch": (None, [_i32, _i32, _i32, C.c_int64]),
+    "mc_sm100_debug_set_chain": (None, [_i32]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -327,6 +328,11 @@ def hint_next_weights(w, nbytes=None):
         lib().mc_sm100_hint_next_weights(None, 0)
     else:
         lib().mc_sm100_hint_next_weights(_p(w), int(nbytes if nbytes is not None else w.numel() * w.element_size()))
+
+
+def debug_set_chain(on: bool) -> None:
+    """M = 1 steps of a one-GPU stack as one persistent kernel, or (default) one kernel per linear."""
+    lib().mc_sm100_debug_set_chain(1 if on else 0)
 
 
 def debug_set_prefetch(mode=-1, chunk_bytes=-1, evict_first=-1, cap_bytes=0):

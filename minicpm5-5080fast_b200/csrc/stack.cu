@@ -13,7 +13,12 @@
 #include <new>
 
 #include "common.cuh"
+#include "decode_chain.cuh"
+#include "gemv_rows.cuh"
 #include "skinny_gemm.cuh"
+
+#include <atomic>
+#include <vector>
 
 namespace mcl {
 
@@ -94,6 +99,9 @@ static Layout make_layout(const mc_sm100_stack_desc_t* d) {
 // activation scratch (bf16 unless noted), all 256-byte aligned
 struct Scratch {
     size_t x, res_a, res_b, h, qkv, ctx, o, mid, down, logits, stage, tokens, vals, sync, total;
+    // one-launch M = 1 chain (one GPU): its table of linears (64 bytes each), their arrival counters and the
+    // four tagged vectors (qkv, o, mid, down: one 32-bit word per element) the linears hand to one another
+    size_t chain_table, chain_arrivals, chain_buf[4];
 };
 
 static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
@@ -109,6 +117,11 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
                           // (bounded waits of any kernel of a step), [2] shard token, [3] shard value, [5] gather epoch,
                           // [6] count of batched sharded steps + 1; peer address tables (8 x u64 each) at bytes 64 pairs,
                           // 128 pair counters of M = 1 steps, 192 pair counters of batched steps, 256.. batched buffers
+                          // [8] count of one-launch M = 1 steps + 1, [9] arrival ticket of that kernel's token reduction
+    s.chain_table = take(((size_t)d->layers * 4 + 1) * 64);
+    s.chain_arrivals = take(((size_t)d->layers * 4 + 1) * 4);
+    const size_t cdims[4] = {d->qkv_rows, H, d->inter, H};
+    for (int k = 0; k < 4; ++k) s.chain_buf[k] = take(cdims[k] * 4);
     s.total = off;
     return s;
 }
@@ -163,7 +176,15 @@ struct mc_sm100_stack {
     cudaGraphExec_t graph[65];     // per batch size, captured lazily
     cudaStream_t graph_stream[65];
     int32_t* h_status;             // pinned host word the failure word is read into after a host step
+    uint32_t chain_slot;           // ring slot size of the one-launch M = 1 chain; 0 = shapes do not fit, per-linear kernels
+    uint32_t chain_kmax;
+    uint32_t chain_nshapes, chain_shape_rows[CHAIN_SHAPES], chain_shape_gran[CHAIN_SHAPES], chain_shape_rpu[CHAIN_SHAPES];
 };
+
+// 1: an M = 1 step of a one-GPU stack is one persistent kernel; 0 (default): one kernel per linear.  Measured on
+// the benchmark's 40-layer stream: 1.245 ms against 1.097 ms (bf16), 1.219 against 0.892 ms (e4m3): the
+// hand-over of a vector between the CTAs costs ~2 us per linear and the ring then refills in bursts.
+static std::atomic<int> g_chain_mode{0};
 
 // Weights of section `which` of layer `layer` as a prefetch hint for the launch that follows.
 static void hint(const mc_sm100_stack* st, uint32_t layer, uint32_t which);
@@ -373,6 +394,27 @@ static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint3
     mc_status_t rc = MC_OK;
     if (d.world > 1u) return M == 1 ? run_step_sharded(st, d_x, d_tokens, stream) : run_step_sharded_batched(st, d_x, M, d_tokens, stream);
 #define STEP(call) do { rc = (call); if (rc != MC_OK) return rc; } while (0)
+    if (M == 1 && st->chain_slot != 0u && g_chain_mode.load(std::memory_order_relaxed) != 0) {
+        uint32_t* sync = reinterpret_cast<uint32_t*>(st->s + st->scr.sync);
+        ChainArgs a{};
+        a.table = reinterpret_cast<const ChainLinear*>(st->s + st->scr.chain_table);
+        a.count = 4u * d.layers + 1u;
+        a.H = H; a.kmax = st->chain_kmax; a.slot_bytes = st->chain_slot;
+        a.nshapes = st->chain_nshapes;
+        for (uint32_t i = 0; i < CHAIN_SHAPES; ++i) {
+            a.shape_rows[i] = st->chain_shape_rows[i]; a.shape_gran[i] = st->chain_shape_gran[i]; a.shape_rpu[i] = st->chain_shape_rpu[i];
+        }
+        for (int k = 0; k < 4; ++k) a.bufs[k] = reinterpret_cast<uint32_t*>(st->s + st->scr.chain_buf[k]);
+        a.arrivals = reinterpret_cast<uint32_t*>(st->s + st->scr.chain_arrivals);
+        a.x_in = d_x; a.logits = logits;
+        a.stage_val = reinterpret_cast<float*>(stage);
+        a.stage_idx = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(stage) + 4096);
+        a.token = d_tokens; a.token_val = vals;
+        a.step = sync + 8; a.ticket = sync + 9; a.status = reinterpret_cast<int32_t*>(sync + 1);
+        a.timeout_ns = st->timeout_ns ? st->timeout_ns : kShardWaitDefaultNs;
+        a.eps = d.eps;
+        return decode_chain_launch(fp8 ? 1 : 2, a, stream);
+    }
     if (M == 1) {
         // fused chain: residual add + RMSNorm live in the GEMV prologues, SwiGLU in the gate_up epilogue
         const uint16_t* res_in = d_x;
@@ -433,7 +475,62 @@ static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint3
     return MC_OK;
 }
 
+// The table of the one-launch M = 1 chain: per layer qkv (residual + norm prologue), o, gate_up (residual + norm
+// prologue, SwiGLU epilogue), down, then the lm_head (final norm, greedy token).  Leaves chain_slot 0 when the
+// shapes do not fit the kernel's shared memory or its argmax staging.
+static cudaError_t chain_setup(mc_sm100_stack* st) {
+    const mc_sm100_stack_desc_t& d = st->desc;
+    const bool fp8 = d.precision == 2u;
+    const int wb = fp8 ? 1 : 2;
+    const uint32_t H = d.hidden, I = d.inter;
+    const uint32_t kmax = H > I ? H : I;
+    const uint32_t unit_max = (2u * H > I ? 2u * H : I) * (uint32_t)wb;      // a gate/up pair, or one down row
+    if ((uint32_t)sm_count() * 8u > 4096u || mc_sm100_argmax_stage_bytes(1) < 8192u) return cudaSuccess;
+    const uint32_t slot = chain_slot_bytes(wb, H, kmax, unit_max);
+    if (slot == 0u) return cudaSuccess;
+    std::vector<ChainLinear> t;
+    bool too_many = false;
+    uint32_t nshapes = 0, srows[CHAIN_SHAPES] = {0}, sgran[CHAIN_SHAPES] = {1, 1, 1, 1, 1, 1, 1, 1}, srpu[CHAIN_SHAPES] = {1, 1, 1, 1, 1, 1, 1, 1};
+    auto add = [&](uint32_t l, uint32_t wsec, uint32_t ssec, uint32_t nsec, uint32_t N, uint32_t K, uint32_t pro, uint32_t epi,
+                   uint32_t in_buf, uint32_t out_buf) {
+        ChainLinear c{};
+        c.w = reinterpret_cast<const uint8_t*>(sec(st, l, wsec));
+        c.scale = fp8 ? reinterpret_cast<const float*>(sec(st, l, ssec)) : nullptr;
+        c.norm_w = pro == PRO_RESNORM ? reinterpret_cast<const uint16_t*>(sec(st, l, nsec)) : nullptr;
+        c.N = N; c.K = K; c.pro = pro; c.epi = epi; c.in_buf = in_buf; c.out_buf = out_buf;
+        c.rows_per_unit = chain_rows_per_unit(wb, K, epi, slot);
+        const uint32_t gran = epi == EPI_SWIGLU ? 2u : 1u;
+        uint32_t sid = 0;
+        while (sid < nshapes && !(srows[sid] == N && sgran[sid] == gran && srpu[sid] == c.rows_per_unit)) ++sid;
+        if (sid == nshapes && nshapes < CHAIN_SHAPES) { srows[sid] = N; sgran[sid] = gran; srpu[sid] = c.rows_per_unit; ++nshapes; }
+        c.shape = sid;
+        too_many = too_many || sid >= CHAIN_SHAPES;
+        t.push_back(c);
+    };
+    for (uint32_t l = 0; l < d.layers; ++l) {
+        add(l, SEC_QKV, SEC_QKV_SCALE, SEC_NORM1, d.qkv_rows, H, PRO_RESNORM, EPI_STORE, l == 0 ? CHAIN_IN_X : 3u, 0u);
+        add(l, SEC_O, SEC_O_SCALE, 0, H, H, PRO_NONE, EPI_STORE, 0u, 1u);       // activation: the first H words of qkv
+        add(l, SEC_GATE_UP, SEC_GATE_UP_SCALE, SEC_NORM2, 2u * I, H, PRO_RESNORM, EPI_SWIGLU, 1u, 2u);
+        add(l, SEC_DOWN, SEC_DOWN_SCALE, 0, H, I, PRO_NONE, EPI_STORE, 2u, 3u);
+    }
+    add(0, SEC_LM_HEAD, SEC_LM_HEAD_SCALE, SEC_FINAL_NORM, d.vocab, H, PRO_RESNORM, EPI_ARGMAX, 3u, CHAIN_IN_NONE);
+    if (too_many) return cudaSuccess;
+    cudaError_t e = cudaMemcpy(st->s + st->scr.chain_table, t.data(), t.size() * sizeof(ChainLinear), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(st->s + st->scr.chain_arrivals, 0, t.size() * 4);
+    for (int k = 0; k < 4 && e == cudaSuccess; ++k) {
+        const size_t dims[4] = {d.qkv_rows, H, I, H};
+        e = cudaMemset(st->s + st->scr.chain_buf[k], 0, dims[k] * 4);       // tag 0: not what the first steps wait for
+    }
+    if (e == cudaSuccess) {
+        st->chain_slot = slot; st->chain_kmax = kmax; st->chain_nshapes = nshapes;
+        for (uint32_t i = 0; i < CHAIN_SHAPES; ++i) { st->chain_shape_rows[i] = srows[i]; st->chain_shape_gran[i] = sgran[i]; st->chain_shape_rpu[i] = srpu[i]; }
+    }
+    return e;
+}
+
 extern "C" {
+
+void mc_sm100_debug_set_chain(int32_t on) { g_chain_mode.store(on != 0 ? 1 : 0, std::memory_order_relaxed); }
 
 mc_status_t mc_sm100_stack_sizes(const mc_sm100_stack_desc_t* desc, uint64_t* weight_bytes, uint64_t* scratch_bytes) {
     clear_error();
@@ -483,8 +580,11 @@ mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_wei
     // control words of the scratch arena: step counters 1, failure word 0 (a sharded stack sets
     // them again, with its peer tables, when the exchange region is bound)
     uint32_t words[256] = {0};
-    words[0] = 1u; words[6] = 1u;
+    words[0] = 1u; words[6] = 1u; words[8] = 1u;
     cudaError_t e = cudaMemcpy(st->s + st->scr.sync, words, sizeof(words), cudaMemcpyHostToDevice);
+    st->chain_slot = 0;
+    st->chain_kmax = 0;
+    if (e == cudaSuccess && world_of(desc) == 1u) e = chain_setup(st);
     if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&st->h_status), 64, cudaHostAllocDefault);
     if (e != cudaSuccess) {
         set_error("mc_sm100_stack_create: %s", cudaGetErrorString(e));

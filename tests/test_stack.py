@@ -201,5 +201,22 @@ def test_stack_at_benchmark_dimensions(pkg, fp8, M):
             assert np.array_equal(again, got)
         finally:
             pkg.debug_set_prefetch(mode=0)
+        if M == 1:
+            # the one-launch form of the M = 1 step (off by default): same bits, same token, three steps in a row
+            # (its arrival counters and tags carry over from step to step), no wait ran out
+            pkg.debug_set_chain(True)
+            try:
+                dx = torch.from_numpy(x.view(np.int16)).cuda()
+                dtok = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+                for _ in range(3):
+                    scratch[off:off + V * 2].zero_()
+                    pkg.stack_step(st, dx, 1, dtok)
+                    torch.cuda.synchronize()
+                    chain = scratch[off:off + V * 2].cpu().numpy().view(np.uint16).reshape(1, V)
+                    assert np.array_equal(chain, got)
+                    assert int(dtok.item()) == int(toks[0][0])
+                assert pkg.stack_exchange_status(st, stream) == 0
+            finally:
+                pkg.debug_set_chain(False)
     finally:
         pkg.stack_destroy(st)
