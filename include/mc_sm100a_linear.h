@@ -604,6 +604,10 @@ MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
 MC_SM100_API void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes, int32_t evict_first,
                                               int64_t cap_bytes);
 
+/* Host-only self-test of the per-device bookkeeping behind the kernels' shared-memory opt-in (one entry per
+ * device, raised once per device and size, safe under racing host threads); makes no CUDA call.  0 = passed. */
+MC_SM100_API int32_t mc_sm100_debug_optin_selftest(void);
+
 /* A/B hook (process-wide): on != 0 runs an M = 1 step of a one-GPU stack as ONE persistent kernel
  * (every linear of every layer and the lm_head; weights streamed through a shared-memory ring that
  * does not stop at the dependencies between linears; outputs handed from CTA to CTA as tagged words

@@ -115,6 +115,7 @@ SIGNATURES = {
     "mc_sm100_hint_next_weights": (None, [_vp, C.c_uint64]),
     "mc_sm100_debug_set_prefetch": (None, [_i32, _i32, _i32, C.c_int64]),
     "mc_sm100_debug_set_chain": (None, [_i32]),
+    "mc_sm100_debug_optin_selftest": (_i32, []),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }

@@ -35,13 +35,19 @@ struct SmemOptIn {
     cudaError_t ensure(Kern kern, size_t bytes) {
         if (bytes <= 48u * 1024u) return cudaSuccess;
         int dev = 0;
-        cudaError_t e = cudaGetDevice(&dev);
+        const cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
+        return ensure_on(dev, bytes, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); });
+    }
+    // the bookkeeping alone: `raise` performs the opt-in on device `dev` (a fake in the host-side self-test)
+    template <typename Raise>
+    cudaError_t ensure_on(int dev, size_t bytes, Raise raise) {
+        if (bytes <= 48u * 1024u) return cudaSuccess;
         if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
         if (set[dev].load(std::memory_order_acquire) >= bytes) return cudaSuccess;
         std::lock_guard<std::mutex> lock(mu);
         if (set[dev].load(std::memory_order_relaxed) >= bytes) return cudaSuccess;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        const cudaError_t e = raise();
         if (e == cudaSuccess) set[dev].store((uint32_t)bytes, std::memory_order_release);
         return e;
     }

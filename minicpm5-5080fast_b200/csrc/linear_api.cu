@@ -2,6 +2,7 @@
 // the reference launchers' style, kernel selection, and the few helper kernels
 // that are not part of the streaming GEMV family.
 #include <atomic>
+#include <thread>
 #include <cstdarg>
 #include <cstring>
 
@@ -316,6 +317,33 @@ void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes, int32_t evic
     if (chunk_bytes >= 128 && chunk_bytes <= (1 << 20)) g_pf_chunk.store((uint32_t)chunk_bytes & ~127u);
     if (evict_first >= 0) g_pf_evict_first.store(evict_first ? 1u : 0u);
     if (cap_bytes > 0) g_pf_cap.store((uint64_t)cap_bytes);
+}
+
+// Host-only check of the per-device shared-memory opt-in bookkeeping (no CUDA call is made): returns 0, or the
+// number of the expectation that failed.
+int32_t mc_sm100_debug_optin_selftest(void) {
+    static SmemOptIn o;                       // zero-initialised
+    std::atomic<int> raised[kMaxDevices];
+    for (auto& r : raised) r.store(0);
+    auto on = [&](int dev, size_t bytes, cudaError_t result = cudaSuccess) {
+        return o.ensure_on(dev, bytes, [&] { raised[dev].fetch_add(1); return result; });
+    };
+    if (on(0, 40u * 1024u) != cudaSuccess || raised[0] != 0) return 1;          // below 48 KB: nothing to raise
+    if (on(0, 100u * 1024u) != cudaSuccess || raised[0] != 1) return 2;         // first use on device 0
+    if (on(0, 100u * 1024u) != cudaSuccess || raised[0] != 1) return 3;         // remembered
+    if (on(0, 64u * 1024u) != cudaSuccess || raised[0] != 1) return 4;          // a smaller request is covered
+    if (on(1, 100u * 1024u) != cudaSuccess || raised[1] != 1) return 5;         // another device: raised again
+    if (on(0, 200u * 1024u) != cudaSuccess || raised[0] != 2) return 6;         // a larger request raises again
+    if (on(63, 100u * 1024u) != cudaSuccess || raised[63] != 1) return 7;
+    if (on(64, 100u * 1024u) != cudaErrorInvalidDevice || on(-1, 100u * 1024u) != cudaErrorInvalidDevice) return 8;
+    if (on(2, 100u * 1024u, cudaErrorInvalidValue) != cudaErrorInvalidValue || o.recorded(2) != 0u) return 9;   // a failed raise is not remembered
+    if (on(2, 100u * 1024u) != cudaSuccess || raised[2] != 2) return 10;
+    // host threads racing for one device: exactly one raise
+    std::thread th[8];
+    for (auto& t : th) t = std::thread([&] { for (int i = 0; i < 1000; ++i) (void)on(5, 150u * 1024u); });
+    for (auto& t : th) t.join();
+    if (raised[5] != 1 || o.recorded(5) != 150u * 1024u) return 11;
+    return 0;
 }
 
 mc_status_t mc_sm100_device_check(int32_t* out_sm_count, uint64_t* out_l2_bytes,

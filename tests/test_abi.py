@@ -58,3 +58,10 @@ def test_argument_validation_needs_no_gpu(pkg):
     assert lib.mc_sm100_decode_gemv(16, 16, 16, 8, 24, 2, 2, 16, None, 0) == pkg.MC_E_INVALID_ARGUMENT
     assert lib.mc_sm100_decode_gemv(16, 16, 16, 8, 32, 2, 2, None, None, 0) == pkg.MC_E_INVALID_ARGUMENT
     assert lib.mc_sm100_argmax_stage_bytes(1) >= 8 * 1024
+
+
+def test_shared_memory_opt_in_bookkeeping_is_per_device(pkg):
+    """A process that drives several GPUs must raise a kernel's dynamic shared memory once on EVERY device (the
+    attribute is per device), remember it per device and size, and survive racing host threads: the library's
+    host-only self-test of that bookkeeping (no CUDA call, no GPU needed)."""
+    assert pkg.lib().mc_sm100_debug_optin_selftest() == 0
