@@ -154,6 +154,30 @@ struct ShardIO {
 
 constexpr unsigned long long kShardWaitDefaultNs = 1000ull * 1000ull * 1000ull;   // 1 s
 
+// Batched (M > 1) sharded steps: the tensor-core GEMM stores its [M, rows] result straight into column
+// block `rank` of EVERY rank's [M, width] activation buffer (peer-mapped) as TAGGED 64-bit words: two
+// adjacent bf16 in the low half, the exchange's 32-bit sequence number (*step - 1) * layers + lsel
+// (never 0; the buffers start zeroed) in the high half.  One relaxed 8-byte store per pair and peer: no
+// fence, no flag, no atomics (measured on two GPUs: the same exchange behind a system-scope fence and an
+// arrival counter per CTA costs ~6 us per linear; the fence waits for the stores' round trip over NVLink).
+// The consumer re-reads a word until its tag is current.  world = 0: plain bf16 store to the local y.
+struct PeerOut {
+    uint64_t base[8];           // rank p's [M, pitch] buffer of 64-bit words as mapped here ([rank] = own)
+    const uint32_t* step;       // device word >= 1: index of the running step of this kind
+    uint32_t world, pitch, col0;   // pitch and col0 in WORDS (pairs of elements)
+    uint32_t layers, lsel;
+};
+// The consumer's side: words == nullptr: the operand is plain bf16.
+struct TaggedIn {
+    const uint64_t* words;      // [rows, pitch] tagged words
+    const uint32_t* step;
+    uint32_t pitch;             // words per row
+    uint32_t layers, lsel;
+    uint32_t reserved;
+    uint64_t timeout_ns;
+    int32_t* status;            // sticky failure word
+};
+
 // Checks a caller's exchange descriptor and fills the kernel-side form.  `outs` = output
 // elements this rank produces; push = false for kernels whose output stays local.
 inline mc_status_t shard_io_to_args(const char* who, const mc_sm100_shard_io_t* io, uint32_t outs, bool push, ShardIO& sh) {
@@ -337,6 +361,31 @@ __device__ __forceinline__ void ld_tagged8(const uint32_t* src, uint32_t tag, co
     }
 }
 
+// One tagged word (two bf16), re-read past L1 until its tag is current.  Bounded and sticky like ld_tagged8.
+__device__ __forceinline__ uint32_t ld_tagged_pair(const uint64_t* src, uint32_t tag, const TaggedIn& t) {
+    uint64_t t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        uint64_t w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+        if ((uint32_t)(w >> 32) == tag) return (uint32_t)w;
+        if ((spins & 31u) == 0u) {
+            if (*reinterpret_cast<volatile int32_t*>(t.status) != 0) return (uint32_t)w;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > t.timeout_ns) { *reinterpret_cast<volatile int32_t*>(t.status) = 1; return (uint32_t)w; }
+        }
+    }
+}
+
 #endif  // __CUDACC__
+
+// residual add + RMSNorm over M rows whose addend is a tagged gathered buffer (add.words != nullptr, d_add ignored);
+// when d_advance is given the kernel adds 1 to that word at its end.  detag_rows: tagged words -> plain bf16
+// [rows, cols] (cols even), the operand form the tensor-core GEMM's TMA loads need.  Both are defined beside
+// mc_sm100_residual_rmsnorm_rows.
+mc_status_t residual_rmsnorm_rows_tagged(uint16_t* d_res, const uint16_t* d_add, const uint16_t* d_norm_w, uint16_t* d_out,
+                                         uint32_t rows, uint32_t n, float eps, const TaggedIn& add, uint32_t* d_advance,
+                                         cudaStream_t stream, bool pdl);
+mc_status_t detag_rows(const TaggedIn& in, uint16_t* d_out, uint32_t rows, uint32_t cols, cudaStream_t stream, bool pdl);
 
 }  // namespace mcl

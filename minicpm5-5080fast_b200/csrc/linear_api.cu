@@ -260,10 +260,43 @@ __global__ void post_scale_rows_kernel(uint16_t* __restrict__ y, const float* __
 // CTA per row (semantics of native/kernels/sm120/rmsnorm.cu:130-166).
 __global__ void residual_rmsnorm_rows_kernel(uint16_t* __restrict__ res, const uint16_t* __restrict__ add,
                                              const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
-                                             uint32_t n, float eps) {
+                                             uint32_t n, float eps, const TaggedIn tin, uint32_t* advance) {
     __shared__ float part[8];
     pdl_trigger();
     pdl_wait();
+    if (tin.words != nullptr) {
+        // the addend is a gathered buffer of tagged words (two elements each): poll, add, round -- a thread owns
+        // the same pairs in the second pass below
+        const uint32_t tag = (*tin.step - 1u) * tin.layers + tin.lsel;
+        const uint64_t* tr = tin.words + (size_t)blockIdx.x * tin.pitch;
+        uint16_t* rr2 = res + (size_t)blockIdx.x * n;
+        uint16_t* orow2 = out + (size_t)blockIdx.x * n;
+        float ss2 = 0.f;
+        for (uint32_t i = threadIdx.x; i < n / 2u; i += blockDim.x) {
+            const uint32_t ad = ld_tagged_pair(tr + i, tag, tin);
+            const uint32_t rv = reinterpret_cast<const uint32_t*>(rr2)[i];
+            const uint16_t r0 = f32_to_bf16_bits(__uint_as_float(rv << 16) + __uint_as_float(ad << 16));
+            const uint16_t r1 = f32_to_bf16_bits(__uint_as_float(rv & 0xFFFF0000u) + __uint_as_float(ad & 0xFFFF0000u));
+            reinterpret_cast<uint32_t*>(rr2)[i] = (uint32_t)r0 | ((uint32_t)r1 << 16);
+            const float f0 = __uint_as_float((uint32_t)r0 << 16), f1 = __uint_as_float((uint32_t)r1 << 16);
+            ss2 = fmaf(f0, f0, ss2);
+            ss2 = fmaf(f1, f1, ss2);
+        }
+        ss2 = warp_sum(ss2);
+        if ((threadIdx.x & 31u) == 0u) part[threadIdx.x >> 5] = ss2;
+        __syncthreads();
+        float tot2 = 0.f;
+        for (uint32_t k = 0; k < blockDim.x / 32u; ++k) tot2 += part[k];
+        const float inv2 = 1.0f / sqrtf(tot2 / (float)n + eps);
+        for (uint32_t i = threadIdx.x; i < n / 2u; i += blockDim.x) {
+            const uint32_t rv = reinterpret_cast<const uint32_t*>(rr2)[i], wv = reinterpret_cast<const uint32_t*>(w)[i];
+            const uint16_t o0 = f32_to_bf16_bits(__uint_as_float(rv << 16) * inv2 * __uint_as_float(wv << 16));
+            const uint16_t o1 = f32_to_bf16_bits(__uint_as_float(rv & 0xFFFF0000u) * inv2 * __uint_as_float(wv & 0xFFFF0000u));
+            reinterpret_cast<uint32_t*>(orow2)[i] = (uint32_t)o0 | ((uint32_t)o1 << 16);
+        }
+        if (advance != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *advance = *advance + 1u;
+        return;
+    }
     uint16_t* rr = res + (size_t)blockIdx.x * n;
     const uint16_t* ar = add ? add + (size_t)blockIdx.x * n : nullptr;
     uint16_t* orow = out + (size_t)blockIdx.x * n;
@@ -285,9 +318,38 @@ __global__ void residual_rmsnorm_rows_kernel(uint16_t* __restrict__ res, const u
     const float inv = 1.0f / sqrtf(tot / (float)n + eps);
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x)   // each thread re-reads only what it wrote
         orow[i] = f32_to_bf16_bits(__uint_as_float((uint32_t)rr[i] << 16) * inv * __uint_as_float((uint32_t)w[i] << 16));
+    if (advance != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *advance = *advance + 1u;
+}
+
+// Tagged gathered buffer -> plain bf16 [rows, cols]: the operand form the tensor-core GEMM's TMA loads need.
+__global__ void detag_rows_kernel(const TaggedIn tin, uint16_t* __restrict__ out, uint32_t cols) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t tag = (*tin.step - 1u) * tin.layers + tin.lsel;
+    const uint64_t* tr = tin.words + (size_t)blockIdx.y * tin.pitch;
+    uint32_t* orow = reinterpret_cast<uint32_t*>(out + (size_t)blockIdx.y * cols);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < cols / 2u; i += gridDim.x * blockDim.x)
+        orow[i] = ld_tagged_pair(tr + i, tag, tin);
 }
 
 }  // namespace mcl
+
+mc_status_t mcl::residual_rmsnorm_rows_tagged(uint16_t* d_res, const uint16_t* d_add, const uint16_t* d_norm_w, uint16_t* d_out,
+                                              uint32_t rows, uint32_t n, float eps, const TaggedIn& add, uint32_t* d_advance,
+                                              cudaStream_t stream, bool pdl) {
+    if (add.words != nullptr && (n & 1u) != 0u) { set_error("residual_rmsnorm_rows: a tagged addend needs an even width"); return MC_E_INVALID_ARGUMENT; }
+    (void)launch(residual_rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, stream, pdl, d_res, d_add, d_norm_w, d_out, n, eps, add, d_advance);
+    MCL_CHECK_LAUNCH("residual_rmsnorm_rows");
+    return MC_OK;
+}
+
+mc_status_t mcl::detag_rows(const TaggedIn& in, uint16_t* d_out, uint32_t rows, uint32_t cols, cudaStream_t stream, bool pdl) {
+    if (in.words == nullptr || d_out == nullptr || rows == 0 || cols == 0 || (cols & 1u) != 0u) { set_error("detag_rows: invalid args"); return MC_E_INVALID_ARGUMENT; }
+    const uint32_t gx = (cols / 2u + 255u) / 256u;
+    (void)launch(detag_rows_kernel, dim3(gx < 16u ? gx : 16u, rows), dim3(256), 0, stream, pdl, in, d_out, cols);
+    MCL_CHECK_LAUNCH("detag_rows");
+    return MC_OK;
+}
 
 using namespace mcl;
 
@@ -666,10 +728,7 @@ mc_status_t mc_sm100_residual_rmsnorm_rows(uint16_t* d_res, const uint16_t* d_ad
         set_error("mc_sm100_residual_rmsnorm_rows: invalid args (rows=%u n=%u)", rows, n);
         return MC_E_INVALID_ARGUMENT;
     }
-    (void)launch(residual_rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, pdl != 0, d_res, d_add,
-                 d_norm_w, d_out, n, eps);
-    MCL_CHECK_LAUNCH("residual_rmsnorm_rows");
-    return MC_OK;
+    return residual_rmsnorm_rows_tagged(d_res, d_add, d_norm_w, d_out, rows, n, eps, TaggedIn{}, nullptr, (cudaStream_t)stream, pdl != 0);
 }
 
 // ---- greedy -------------------------------------------------------------------------

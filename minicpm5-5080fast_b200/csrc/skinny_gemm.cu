@@ -133,6 +133,7 @@ struct SkinnyArgs {
     uint32_t swiglu;        // rows 2j / 2j+1 are gate_j / up_j: store silu(g)*u
     uint32_t op_stages, raw_stages;  // ring depths (<= 8), chosen by the launcher from the grid size
     int32_t* status;        // optional device word set to 1 when a bounded wait ran out (the caller's failure word)
+    PeerOut out;            // sharded step: the result goes to every rank's activation buffer as tagged words (world = 0: to y)
     PrefetchArgs pf;        // L2 prefetch of the next kernel's weights (all zero = off)
 };
 
@@ -373,6 +374,15 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     {
         const bool failed = *abortp != 0;
         const uint32_t nbase = (uint32_t)n0 + rank * per_n;          // first feature this CTA finishes
+        // sharded step: two adjacent finished values (row m, columns c and c + 1 of the result, c even) travel
+        // as one tagged 64-bit word to every rank's gathered buffer
+        const uint64_t out_tag = a.out.world != 0u ? (uint64_t)((*a.out.step - 1u) * a.out.layers + a.out.lsel) << 32 : 0ull;
+        auto put_pair = [&](uint32_t m, uint32_t c, uint16_t v0, uint16_t v1) {
+            const uint64_t word = out_tag | ((uint64_t)v1 << 16) | (uint64_t)v0;
+            for (uint32_t p = 0; p < a.out.world; ++p)
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;"
+                             ::"l"(reinterpret_cast<uint64_t*>(a.out.base[p]) + (size_t)m * a.out.pitch + a.out.col0 + (c >> 1)), "l"(word) : "memory");
+        };
         auto partial_sum = [&](uint32_t n_rel, uint32_t m) {
             float acc = 0.f;
             for (uint32_t r = 0; r < S; ++r) {    // rank order: bit-reproducible
@@ -382,7 +392,38 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             return acc;
         };
-        if (!a.swiglu) {
+        auto finish = [&](uint32_t n_rel, uint32_t m) {       // one plain output element, scaled and rounded
+            float acc = partial_sum(n_rel, m);
+            const uint32_t n = nbase + n_rel;
+            if (n < a.N) {
+                if (a.w_scale != nullptr) acc *= a.w_scale[n];
+                if (MODE == SKINNY_W8A8) acc *= a.x_scale[m];
+            }
+            return f32_to_bf16_bits(acc);
+        };
+        auto finish_swiglu = [&](uint32_t p, uint32_t m) {    // one SwiGLU output element from rows 2p, 2p + 1 of the slice
+            float gt = partial_sum(2u * p, m), up = partial_sum(2u * p + 1u, m);
+            const uint32_t n = nbase + 2u * p;
+            if (n + 1 < a.N) {
+                if (a.w_scale != nullptr) { gt *= a.w_scale[n]; up *= a.w_scale[n + 1]; }
+                if (MODE == SKINNY_W8A8) { gt *= a.x_scale[m]; up *= a.x_scale[m]; }
+            }
+            const float gb = __uint_as_float((uint32_t)f32_to_bf16_bits(gt) << 16);
+            const float ub = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
+            return f32_to_bf16_bits(swiglu_f32(gb, ub));
+        };
+        if (a.out.world != 0u) {
+            // pairs of adjacent outputs (the slice holds an even number of them, starting at an even column)
+            const uint32_t outs = a.swiglu ? per_n / 2u : per_n, obase = a.swiglu ? nbase >> 1 : nbase, olimit = a.swiglu ? a.N / 2u : a.N;
+            for (uint32_t idx = tid; idx < (outs / 2u) * a.M; idx += kThreads) {
+                const uint32_t m = idx / (outs / 2u), c_rel = 2u * (idx % (outs / 2u)), c = obase + c_rel;
+                if (c < olimit && !failed) {
+                    const uint16_t v0 = a.swiglu ? finish_swiglu(c_rel, m) : finish(c_rel, m);
+                    const uint16_t v1 = c + 1u < olimit ? (a.swiglu ? finish_swiglu(c_rel + 1u, m) : finish(c_rel + 1u, m)) : (uint16_t)0;
+                    put_pair(m, c, v0, v1);
+                }
+            }
+        } else if (!a.swiglu) {
             for (uint32_t idx = tid; idx < per_n * a.M; idx += kThreads) {
                 const uint32_t m = idx / per_n, n_rel = idx % per_n, n = nbase + n_rel;   // n fastest: coalesced stores
                 float acc = partial_sum(n_rel, m);
@@ -572,7 +613,7 @@ size_t skinny_workspace_bytes(uint32_t, uint32_t, uint32_t) { return 0; }
 
 mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uint16_t* x, const float* x_scale,
                         uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu, cudaStream_t stream, bool pdl,
-                        uint32_t x_pitch) {
+                        uint32_t x_pitch, const PeerOut* out) {
     if (x_pitch == 0u) x_pitch = K;
     const uint32_t x_elem = mode == SKINNY_W8A8 ? 1u : 2u;
     if (M == 0 || M > 64 || !aligned16(w) || !aligned16(x) || (swiglu && (N & 1u)) || x_pitch < K || ((x_pitch * x_elem) & 15u) != 0u) {
@@ -586,6 +627,7 @@ mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uin
     const uint32_t grid = p.tiles * p.splits;
     a.pf = make_prefetch_args(take_next_weights(), grid);
     a.status = wait_status_sink();
+    if (out != nullptr) a.out = *out;
     // Ring depth: as many stages as fit in ~108 KB, i.e. half an SM's shared memory.  Measured
     // (down_proj 2304 x 5760, chain of calls): with 150 or 200 KB, one CTA per SM, a call takes 14.7 us
     // against 8.8 us at M = 8 and 19.1 against 12.9 us at M = 64, because the next kernel's CTA can then

@@ -21,9 +21,12 @@ size_t skinny_workspace_bytes(uint32_t M, uint32_t N, uint32_t K);
 // e4m3, kind::f8f6f4 (x passed through the uint16_t pointer type unchanged).
 // swiglu: W rows are interleaved (gate_j, up_j); y[M, N/2] = bf16(silu(bf16 g) * bf16 u).
 // x_pitch: elements between consecutive rows of x (0 = K): lets a GEMM read a column block of a wider matrix.
+// out (sharded batched steps): the result goes into every rank's gathered buffer as tagged words instead of y
+// (N, and N / 2 behind the SwiGLU epilogue, must then be even).
 mc_status_t skinny_gemm(int mode, const void* w, const float* w_scale, const uint16_t* x,
                         const float* x_scale, uint16_t* y, uint32_t M, uint32_t N, uint32_t K,
-                        bool swiglu, cudaStream_t stream, bool pdl, uint32_t x_pitch = 0);
+                        bool swiglu, cudaStream_t stream, bool pdl, uint32_t x_pitch = 0,
+                        const PeerOut* out = nullptr);
 
 // 1 when a bounded wait inside the tensor-core kernel ran out since the last query (clears it), -1 on a CUDA error.
 int skinny_take_error();

@@ -117,6 +117,7 @@ static Scratch make_scratch(const mc_sm100_stack_desc_t* d) {
                           // (bounded waits of any kernel of a step), [2] shard token, [3] shard value, [5] gather epoch,
                           // [6] count of batched sharded steps + 1; peer address tables (8 x u64 each) at bytes 64 pairs,
                           // 128 pair counters of M = 1 steps, 192 pair counters of batched steps, 256.. batched buffers
+                          // [7] count of batched sharded steps whose GEMMs do the exchange themselves + 1,
                           // [8] count of one-launch M = 1 steps + 1, [9] arrival ticket of that kernel's token reduction
     s.chain_table = take(((size_t)d->layers * 4 + 1) * 64);
     s.chain_arrivals = take(((size_t)d->layers * 4 + 1) * 4);
@@ -136,6 +137,7 @@ struct Exchange {
     size_t pairs, pair_flags;   // [8][max_batch] x 8 bytes; 8 x uint32 for M = 1 steps, then 8 x uint32 for batched steps
     // batched steps (M > 1): plain bf16 [max_batch, full width] activations + the gather's arrival flags
     size_t bbuf[XK_VECS], bflags;
+    size_t tbuf[XK_VECS];    // the same four activations as tagged 64-bit words (two bf16 + a 32-bit sequence number), written by the GEMMs themselves
     uint32_t width[XK_VECS];
     size_t bytes;
 };
@@ -155,6 +157,7 @@ static Exchange make_exchange(const mc_sm100_stack_desc_t* d) {
     if (d->max_batch > 1u) {
         for (uint32_t k = 0; k < XK_VECS; ++k) { x.bbuf[k] = off; off += align256((size_t)d->max_batch * dims[k] * 2u); }
         x.bflags = off; off += align256(8u * 4u);
+        for (uint32_t k = 0; k < XK_VECS; ++k) { x.tbuf[k] = off; off += align256((size_t)d->max_batch * dims[k] * 4u); }
     }
     x.bytes = off;
     return x;
@@ -324,6 +327,55 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
         return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, l, wsec), (const float*)sec(st, l, ssec), in, part, M, rows, K, sp, 1)
                    : mc_sm100_gemm_bf16(sp, nullptr, 0, M, rows, K, sec(st, l, wsec), in, part);
     };
+    // When every linear of the layer runs on the tensor cores, the GEMM itself stores its result into every rank's
+    // buffer, as tagged words (two bf16 + the exchange's 32-bit sequence number; no fence, no flag).  The norms read
+    // their addend from those words; the two GEMMs whose activation is such a buffer (o_proj, down_proj) get it
+    // through a small kernel that polls the tags and writes plain bf16 for the TMA loads.  No gather kernels.
+    const int mode = fp8 ? SKINNY_W_E4M3 : SKINNY_W_BF16;
+    const int wbytes = fp8 ? 1 : 2;
+    const bool fused = (fp8 ? M >= 4u : M >= 2u) && skinny_shape_ok(sq.rows, H, wbytes) && skinny_shape_ok(sh.rows, H, wbytes) &&
+                       skinny_shape_ok(2u * si.rows, H, wbytes) && skinny_shape_ok(sh.rows, I, wbytes);
+    if (fused) {
+        uint16_t* mid_plain = buf(st->scr.mid);
+        auto out_of = [&](uint32_t k, uint32_t lsel) {
+            PeerOut o{};
+            for (uint32_t p = 0; p < W; ++p) o.base[p] = st->peer[p] + x.tbuf[k];
+            o.step = sync + 7; o.world = W; o.pitch = x.width[k] / 2u; o.col0 = R * x.pitch[k] / 2u; o.layers = L; o.lsel = lsel;
+            return o;
+        };
+        auto in_of = [&](uint32_t k, uint32_t lsel) {
+            TaggedIn t{};
+            t.words = reinterpret_cast<const uint64_t*>(own + x.tbuf[k]);
+            t.step = sync + 7; t.pitch = x.width[k] / 2u; t.layers = L; t.lsel = lsel;
+            t.timeout_ns = st->timeout_ns ? st->timeout_ns : kShardWaitDefaultNs; t.status = status;
+            return t;
+        };
+        auto gemm = [&](uint32_t l, uint32_t wsec, uint32_t ssec, const uint16_t* in, uint32_t rows, uint32_t K, bool swiglu, uint32_t out_kind) {
+            const PeerOut o = out_of(out_kind, l + 1u);
+            return skinny_gemm(mode, sec(st, l, wsec), fp8 ? (const float*)sec(st, l, ssec) : nullptr, in, nullptr, part, M, rows, K, swiglu,
+                               stream, true, 0, &o);
+        };
+        cudaError_t ce = cudaMemcpyAsync(ra, d_x, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, stream);
+        if (ce != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(ce)); return MC_E_CUDA; }
+        for (uint32_t l = 0; l < L; ++l) {
+            // exchange numbers within the step: kind k of layer l is number l + 1 of its kind
+            STEP(residual_rmsnorm_rows_tagged(ra, nullptr, (const uint16_t*)sec(st, l, SEC_NORM1), h, M, H, d.eps,
+                                              l == 0 ? TaggedIn{} : in_of(XK_DOWN, l), nullptr, stream, true));
+            hint(st, l, SEC_O);
+            STEP(gemm(l, SEC_QKV, SEC_QKV_SCALE, h, sq.rows, H, false, XK_QKV));
+            STEP(detag_rows(in_of(XK_QKV, l + 1u), ctx, M, H, stream, true));        // attention stand-in: the first H columns of qkv
+            hint(st, l, SEC_GATE_UP);
+            STEP(gemm(l, SEC_O, SEC_O_SCALE, ctx, sh.rows, H, false, XK_O));
+            STEP(residual_rmsnorm_rows_tagged(ra, nullptr, (const uint16_t*)sec(st, l, SEC_NORM2), h, M, H, d.eps, in_of(XK_O, l + 1u), nullptr, stream, true));
+            hint(st, l, SEC_DOWN);
+            STEP(gemm(l, SEC_GATE_UP, SEC_GATE_UP_SCALE, h, 2u * si.rows, H, true, XK_MID));
+            STEP(detag_rows(in_of(XK_MID, l + 1u), mid_plain, M, I, stream, true));
+            if (l + 1 < L) hint(st, l + 1, SEC_QKV); else hint(st, 0, SEC_LM_HEAD);
+            STEP(gemm(l, SEC_DOWN, SEC_DOWN_SCALE, mid_plain, sh.rows, I, false, XK_DOWN));
+        }
+        // the last norm also moves the step word on: every kernel of this step has read it by then
+        STEP(residual_rmsnorm_rows_tagged(ra, nullptr, (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), h, M, H, d.eps, in_of(XK_DOWN, L), sync + 7, stream, true));
+    } else {
     cudaError_t e = cudaMemcpyAsync(ra, d_x, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, stream);
     if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
     const uint16_t* addend = nullptr;
@@ -345,6 +397,7 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
         addend = full(XK_DOWN);
     }
     STEP(mc_sm100_residual_rmsnorm_rows(ra, addend, (const uint16_t*)sec(st, 0, SEC_FINAL_NORM), h, M, H, d.eps, sp, 1));
+    }
     void* stage = st->s + st->scr.stage;
     int32_t* shard_tok = reinterpret_cast<int32_t*>(st->s + st->scr.tokens);
     float* shard_val = reinterpret_cast<float*>(st->s + st->scr.vals);
@@ -580,7 +633,7 @@ mc_status_t mc_sm100_stack_create(const mc_sm100_stack_desc_t* desc, void* d_wei
     // control words of the scratch arena: step counters 1, failure word 0 (a sharded stack sets
     // them again, with its peer tables, when the exchange region is bound)
     uint32_t words[256] = {0};
-    words[0] = 1u; words[6] = 1u; words[8] = 1u;
+    words[0] = 1u; words[6] = 1u; words[7] = 1u; words[8] = 1u;
     cudaError_t e = cudaMemcpy(st->s + st->scr.sync, words, sizeof(words), cudaMemcpyHostToDevice);
     st->chain_slot = 0;
     st->chain_kmax = 0;
@@ -622,7 +675,7 @@ mc_status_t mc_sm100_stack_bind_exchange(mc_sm100_stack_t st, const uint64_t* h_
     const cudaStream_t s = (cudaStream_t)stream;
     uint32_t words[256] = {0};
     words[0] = 1u;   // step counters start at 1; [1] failure word = 0; [5] gather epoch = 0
-    words[6] = 1u;
+    words[6] = 1u; words[7] = 1u; words[8] = 1u;
     uint64_t* tables = reinterpret_cast<uint64_t*>(words + 16);          // byte 64: pairs, byte 128 / 192: pair counters (M = 1 / batched)
     uint64_t* btables = reinterpret_cast<uint64_t*>(words + 64);         // byte 256 + 64 k: batched buffer k; byte 512: gather flags
     for (uint32_t p = 0; p < W; ++p) {

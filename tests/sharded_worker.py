@@ -67,6 +67,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--rows", type=int, default=1, help="batch rows M")
+    ap.add_argument("--mix", action="store_true", help="second trial with 3 rows: another kernel family (and exchange form) on the same stack")
     args = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -81,7 +82,8 @@ def main():
     fp8 = args.fp8
 
     # the one-GPU stack on this device: the reference for tokens and logits
-    M = args.rows
+    MAXB = args.rows
+    M = MAXB
     d1 = pkg.stack_desc(layers, H, Q, I, V, fp8=fp8, max_batch=M)
     a1, s1 = su.upload(pkg, torch, d1, w, fp8)
     st1 = pkg.stack_create(d1, a1, s1)
@@ -100,6 +102,7 @@ def main():
     lo, hi, _ = sh.shard_rows(V, world, rank)
     ok = True
     for trial in range(4):                                  # eager, capture, replay, replay with a new input
+        M = 3 if (args.mix and trial == 1 and MAXB > 3) else MAXB
         x = onp.seeded_bf16(700 + (trial == 3), (M, H), 1.0)
         hx = torch.from_numpy(x.view(np.int16)).pin_memory()
         t1 = torch.full((M,), -1, dtype=torch.int32).pin_memory()

@@ -219,13 +219,15 @@ def test_peer_argmax_reduces_pairs(pkg, g):
 @pytest.mark.gpu
 @pytest.mark.parametrize("fp8", [False, True])
 def test_sharded_batched_stack_two_gpus(pkg, g, fp8):
-    """M = 8 on two GPUs: per-linear scatter into every rank's [M, width] buffers; logits within tolerance of one GPU."""
+    """M = 8 on two GPUs: the tensor-core GEMMs store into every rank's [M, width] buffers themselves and the consumers wait
+    for their arrival counters; one step with 3 rows in between (e4m3: CUDA-core kernels + gather kernels) on the same stack;
+    logits within tolerance of one GPU."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29743", os.path.join(ROOT, "tests", "sharded_worker.py"), "--rows", "8"] + (["--fp8"] if fp8 else [])
+           "--master-port", "29743", os.path.join(ROOT, "tests", "sharded_worker.py"), "--rows", "8", "--mix"] + (["--fp8"] if fp8 else [])
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "SHARDED-OK" in out.stdout, out.stdout[-2000:]
