@@ -145,8 +145,7 @@ __device__ __forceinline__ void chain_wait(const uint32_t* ctr, uint32_t target,
     }
 }
 
-// One 16-byte unit's worth of activation in registers (bf16: 8 elements; e4m3: 16 elements as f16),
-// and the multiply-accumulate against it: same element -> accumulator assignment and order as mac_wide.
+// One 16-byte unit's worth of activation in registers (bf16: 8 elements; e4m3: 16 elements as f16).
 template <int WB> struct XUnit;
 template <> struct XUnit<2> { uint4 a; };
 template <> struct XUnit<1> { uint4 a, b; };
@@ -161,16 +160,7 @@ __device__ __forceinline__ XUnit<WB> load_x(const uint16_t* xb, const uint16_t* 
     }
     return x;
 }
-__device__ __forceinline__ void mac_x(const WideUnit<2>& w, const XUnit<2>& x, float2& a, float2& b) {
-    const uint32_t xv[4] = {x.a.x, x.a.y, x.a.z, x.a.w};
-#pragma unroll
-    for (int j = 0; j < 4; j += 2) {
-        fma_bf16(a.x, (uint16_t)(w.p[j] & 0xFFFFu), (uint16_t)(xv[j] & 0xFFFFu));
-        fma_bf16(a.y, (uint16_t)(w.p[j] >> 16), (uint16_t)(xv[j] >> 16));
-        fma_bf16(b.x, (uint16_t)(w.p[j + 1] & 0xFFFFu), (uint16_t)(xv[j + 1] & 0xFFFFu));
-        fma_bf16(b.y, (uint16_t)(w.p[j + 1] >> 16), (uint16_t)(xv[j + 1] >> 16));
-    }
-}
+// e4m3 on CUDA cores: same element -> accumulator assignment and order as mac_wide
 __device__ __forceinline__ void mac_x(const WideUnit<1>& w, const XUnit<1>& x, float2& a, float2& b) {
     const uint32_t xv[8] = {x.a.x, x.a.y, x.a.z, x.a.w, x.b.x, x.b.y, x.b.z, x.b.w};
 #pragma unroll
@@ -374,38 +364,37 @@ __global__ void __launch_bounds__(kThreads, 1) decode_chain_kernel(const ChainAr
                 ++my_units;
                 for (uint32_t r = 0; r < nrows; r += 2u) {
                     const bool two = r + 1u < nrows;
-                    float2 acc_a[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, acc_b[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                    // the multiply-accumulate of gemv_fast_kernel, operation for operation.  bf16 (tensor cores): rows r and
+                    // r + 1 are A rows g and 8 + g, every lane takes part in every mma (zeros beyond the row's last unit or
+                    // without a second row)
+                    // bf16: row r in (a01, b01), row r + 1 in (a23, b23).  e4m3 (CUDA cores): row r in (a01, b01) = (acc_a, acc_b)
+                    // of gemv_fast_kernel, row r + 1 in (a23, b23)
+                    MmaAcc md;
+                    md.a01 = md.a23 = md.b01 = md.b23 = make_float2(0.f, 0.f);
                     if (!skip_mac) {
                         const uint8_t* w0 = slot_p + (size_t)r * row_bytes;
                         const uint8_t* w1 = w0 + row_bytes;
+                        auto unit = [&](uint32_t v, const XUnit<WB>& xv) {
+                            const bool in = v < nvec;
+                            const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+                            WideUnit<WB> wu0, wu1;
+                            widen(in ? reinterpret_cast<const uint4*>(w0)[v] : z4, wu0);
+                            widen(in && two ? reinterpret_cast<const uint4*>(w1)[v] : z4, wu1);
+                            if constexpr (WB == 2) {
+                                mac_mma(wu0, &wu1, in ? xv.a : z4, md);
+                            } else if (in) {
+                                mac_x(wu0, xv, md.a01, md.b01);
+                                if (two) mac_x(wu1, xv, md.a23, md.b23);
+                            }
+                        };
                         if (x_in_regs) {
 #pragma unroll
-                            for (int u = 0; u < XR; ++u) {
-                                const uint32_t v = lane + 32u * (uint32_t)u;
-                                if (v < nvec) {
-                                    WideUnit<WB> wu;
-                                    widen(reinterpret_cast<const uint4*>(w0)[v], wu);
-                                    mac_x(wu, xr[u], acc_a[0], acc_b[0]);
-                                    if (two) {
-                                        widen(reinterpret_cast<const uint4*>(w1)[v], wu);
-                                        mac_x(wu, xr[u], acc_a[1], acc_b[1]);
-                                    }
-                                }
-                            }
+                            for (int u = 0; u < XR; ++u) unit(lane + 32u * (uint32_t)u, xr[u]);
                         } else {
 #pragma unroll 3
                             for (uint32_t u = 0; u < per_lane; ++u) {
                                 const uint32_t v = lane + 32u * u;
-                                if (v < nvec) {
-                                    const XUnit<WB> xv = load_x<WB>(xb, xh, v);      // once for both rows
-                                    WideUnit<WB> wu;
-                                    widen(reinterpret_cast<const uint4*>(w0)[v], wu);
-                                    mac_x(wu, xv, acc_a[0], acc_b[0]);
-                                    if (two) {
-                                        widen(reinterpret_cast<const uint4*>(w1)[v], wu);
-                                        mac_x(wu, xv, acc_a[1], acc_b[1]);
-                                    }
-                                }
+                                unit(v, load_x<WB>(xb, xh, v < nvec ? v : 0u));
                             }
                         }
                     }
@@ -413,7 +402,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_chain_kernel(const ChainAr
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const uint32_t row = row0 + r + (uint32_t)i;
-                        float s = warp_sum((acc_a[i].x + acc_a[i].y) + (acc_b[i].x + acc_b[i].y));
+                        float s = WB == 2 ? warp_sum(mma_row(md, i, lane))
+                                          : warp_sum(i == 0 ? (md.a01.x + md.a01.y) + (md.b01.x + md.b01.y) : (md.a23.x + md.a23.y) + (md.b23.x + md.b23.y));
                         if constexpr (WB == 1) {
                             s *= kF16Unscale;
                             if ((fallback || s != s) && row < hi && (i == 0 || two))   // warp-uniform: s is the same in every lane

@@ -100,6 +100,60 @@ __device__ __forceinline__ void mac_wide(const WideUnit<1>& w, const uint16_t* x
     }
 }
 
+// ---- the multiply-accumulate on the tensor cores (mma.sync m16n8k16, fp32 accumulators) ----
+// The post-wait burst on CUDA cores is bound by the integer pipe: fma.rn.f32.bf16 / .f16 take 16-bit
+// operands and every one has to be cut out of its packed register first (4.1 thread instructions per
+// weight, measured; halving the multiplies alone takes 40 us off the 1.1 ms step).  A warp-wide mma
+// multiplies what the lanes already hold, in the layout they hold it: lane (g, t) = (lane / 4, lane % 4)
+// supplies A row g (its own four weights of this mma: registers a0, a2) and B column g (the four
+// matching activations: b0, b1), so D[g][g] is the dot product over the 16 elements of lane group g, and
+// the diagonal of D, accumulated over all mmas, holds the eight groups' partial sums of the row.  A second
+// weight row goes to A rows 8..15 (a1, a3) against the same B: its sums are D[8 + g][g].  The rest of D is
+// cross terms nobody reads.  Products of bf16 / f16 are exact, accumulation is fp32.
+// Measured on the 40-layer stream: bf16 1.097 -> 1.065 ms.  e4m3 does not gain (0.892 -> 0.900 - 0.910 ms, lm_head
+// 53 -> 53 - 60 us: its bound is the hardware conversion of the codes, which stays), so it keeps the CUDA-core form.
+template <int WB> constexpr bool kGemvMma = WB == 2;
+
+__device__ __forceinline__ void mma16816_bf16(float2& d01, float2& d23, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d01.x), "+f"(d01.y), "+f"(d23.x), "+f"(d23.y)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816_f16(float2& d01, float2& d23, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d01.x), "+f"(d01.y), "+f"(d23.x), "+f"(d23.y)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// One 16-byte unit of row 0 (and of row 1 when given) against the matching activations; every lane of the
+// warp takes part (a lane without a unit passes zeros).  Two accumulator sets (A, B) take alternate mmas, so
+// that a row's chain of dependent mmas is half as long; each set: d01 = (D[g][2t], D[g][2t+1]), d23 the same
+// for row 8 + g.
+struct MmaAcc { float2 a01, a23, b01, b23; };
+__device__ __forceinline__ void mac_mma(const WideUnit<2>& w0, const WideUnit<2>* w1, const uint4& x, MmaAcc& d) {
+    mma16816_bf16(d.a01, d.a23, w0.p[0], w1 ? w1->p[0] : 0u, w0.p[1], w1 ? w1->p[1] : 0u, x.x, x.y);
+    mma16816_bf16(d.b01, d.b23, w0.p[2], w1 ? w1->p[2] : 0u, w0.p[3], w1 ? w1->p[3] : 0u, x.z, x.w);
+}
+__device__ __forceinline__ void mac_mma(const WideUnit<1>& w0, const WideUnit<1>* w1, const uint4& xa, const uint4& xc, MmaAcc& d) {
+    const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xc.x, xc.y, xc.z, xc.w};
+#pragma unroll
+    for (int i = 0; i < 4; i += 2) {
+        mma16816_f16(d.a01, d.a23, w0.h[2 * i], w1 ? w1->h[2 * i] : 0u, w0.h[2 * i + 1], w1 ? w1->h[2 * i + 1] : 0u, xv[2 * i], xv[2 * i + 1]);
+        mma16816_f16(d.b01, d.b23, w0.h[2 * i + 2], w1 ? w1->h[2 * i + 2] : 0u, w0.h[2 * i + 3], w1 ? w1->h[2 * i + 3] : 0u, xv[2 * i + 2], xv[2 * i + 3]);
+    }
+}
+// a row's sum in this lane's share: row 0 from (a01, b01), row 1 from (a23, b23)
+__device__ __forceinline__ float mma_row(const MmaAcc& d, int r, uint32_t lane);
+// This lane's element of D's diagonal (0 unless the lane holds one): group g's sum sits in lane (g, g / 2).
+__device__ __forceinline__ float mma_diag(const float2& d, uint32_t lane) {
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    return t == (g >> 1) ? ((g & 1u) ? d.y : d.x) : 0.f;
+}
+__device__ __forceinline__ float mma_row(const MmaAcc& d, int r, uint32_t lane) {
+    return r == 0 ? mma_diag(d.a01, lane) + mma_diag(d.b01, lane) : mma_diag(d.a23, lane) + mma_diag(d.b23, lane);
+}
+
 // Exact e4m3 row against the bf16 copy of x, weights re-read from global memory
 // (cold path: range fallback and rows that hold a NaN code).  Warp-collective.
 __device__ __forceinline__ float fp8_row_exact(const uint8_t* wrow, const uint16_t* xb, uint32_t nvec, uint32_t lane) {
@@ -309,6 +363,38 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
 
     // multiply-accumulate one batch held in `raw` (or in `wide` when it was converted early)
     auto mac_batch = [&](auto& raw, bool use_wide, uint32_t i0, float2 (&acc_a)[R], float2 (&acc_b)[R]) {
+        if constexpr (kGemvMma<WB>) {
+            // tensor cores.  Lanes beyond the row's last unit hold zero weights and pass zero activations.
+            static_assert(R <= 2, "an mma takes two weight rows");
+            // accumulators of the running group: row 0 in (acc_a[0], acc_b[0]), row 1 in (acc_a[1], acc_b[1])
+            MmaAcc md;
+            md.a01 = acc_a[0]; md.b01 = acc_b[0];
+            md.a23 = R == 2 ? acc_a[R - 1] : make_float2(0.f, 0.f); md.b23 = R == 2 ? acc_b[R - 1] : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t v = lane + 32u * (i0 + u);
+                const bool in = v < nvec;
+                WideUnit<WB> w0, w1;
+                if (PRE && use_wide) {
+                    w0 = wide[0][PRE ? u : 0];
+                    if constexpr (R == 2) w1 = wide[PRE ? 1 : 0][PRE ? u : 0];
+                } else {
+                    widen(raw[0][u], w0);
+                    if constexpr (R == 2) widen(raw[R - 1][u], w1);
+                }
+                if constexpr (WB == 2) {
+                    const uint4 x = in ? reinterpret_cast<const uint4*>(xb)[v] : make_uint4(0u, 0u, 0u, 0u);
+                    mac_mma(w0, R == 2 ? &w1 : nullptr, x, md);
+                } else {
+                    const uint4 xa = in ? reinterpret_cast<const uint4*>(xh)[2u * v] : make_uint4(0u, 0u, 0u, 0u);
+                    const uint4 xc = in ? reinterpret_cast<const uint4*>(xh)[2u * v + 1u] : make_uint4(0u, 0u, 0u, 0u);
+                    mac_mma(w0, R == 2 ? &w1 : nullptr, xa, xc, md);
+                }
+            }
+            acc_a[0] = md.a01; acc_b[0] = md.b01;
+            if constexpr (R == 2) { acc_a[R - 1] = md.a23; acc_b[R - 1] = md.b23; }
+            return;
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint32_t v = lane + 32u * (i0 + u);
@@ -333,7 +419,8 @@ __global__ void __launch_bounds__(THREADS, MINB) gemv_fast_kernel(const RowsArgs
         float tot[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            float s = warp_sum((acc_a[r].x + acc_a[r].y) + (acc_b[r].x + acc_b[r].y));
+            float s = kGemvMma<WB> ? warp_sum(mma_diag(acc_a[r], lane) + mma_diag(acc_b[r], lane))
+                               : warp_sum((acc_a[r].x + acc_a[r].y) + (acc_b[r].x + acc_b[r].y));
             if constexpr (WB == 1) {
                 s *= kF16Unscale;
                 const uint32_t row = g * R + r;
