@@ -663,6 +663,8 @@ def set_chain(pkg, on):
 
 def apply_prefetch_env(pkg):
     """MC_PREFETCH="mode[,chunk[,evict_first[,cap_mb]]]" overrides the library's L2-prefetch defaults (A/B runs)."""
+    if os.environ.get("MC_MMA_ROWS") is not None:    # MC_MMA_ROWS=0: bf16 batched linears on the tcgen05 kernel only
+        pkg.debug_set_mma_rows(int(os.environ["MC_MMA_ROWS"]))
     if os.environ.get("MC_CHAIN") is not None:       # MC_CHAIN=0: one kernel per linear instead of the one-launch M = 1 chain
         set_chain(pkg, os.environ["MC_CHAIN"] != "0")
     v = os.environ.get("MC_PREFETCH")
@@ -737,6 +739,9 @@ def kernel_name(workload, dtype, m):
         return "gemv_fast_kernel"
     if dtype == "fp8" and m <= 3:
         return "gemv_rows_kernel"
+    if (dtype == "bf16" and 2 <= m <= 8 and workload in Single.SHAPES and Single.SHAPES[workload][2] == 0
+            and Single.SHAPES[workload][0] <= 16 * 148 and os.environ.get("MC_MMA_ROWS", "8") != "0"):
+        return "gemm_mma_rows_kernel"       # a weight of at most 16 rows per SM: the register-streaming mma.sync kernel
     return "skinny_gemm_kernel"
 
 

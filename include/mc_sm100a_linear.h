@@ -604,6 +604,11 @@ MC_SM100_API void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math);
 MC_SM100_API void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes, int32_t evict_first,
                                               int64_t cap_bytes);
 
+/* A/B hook (process-wide): bf16 batched linears with at most max_m rows (default 8, at most 16; 0 = none) whose
+ * weight has at most 16 rows per SM run on the register-streaming mma.sync kernel (csrc/gemm_mma_rows.cu), the
+ * others on the tcgen05 kernel. */
+MC_SM100_API void mc_sm100_debug_set_mma_rows(int32_t max_m);
+
 /* Host-only self-test of the per-device bookkeeping behind the kernels' shared-memory opt-in (one entry per
  * device, raised once per device and size, safe under racing host threads); makes no CUDA call.  0 = passed. */
 MC_SM100_API int32_t mc_sm100_debug_optin_selftest(void);

@@ -116,6 +116,7 @@ SIGNATURES = {
     "mc_sm100_debug_set_prefetch": (None, [_i32, _i32, _i32, C.c_int64]),
     "mc_sm100_debug_set_chain": (None, [_i32]),
     "mc_sm100_debug_optin_selftest": (_i32, []),
+    "mc_sm100_debug_set_mma_rows": (None, [_i32]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -329,6 +330,11 @@ def hint_next_weights(w, nbytes=None):
         lib().mc_sm100_hint_next_weights(None, 0)
     else:
         lib().mc_sm100_hint_next_weights(_p(w), int(nbytes if nbytes is not None else w.numel() * w.element_size()))
+
+
+def debug_set_mma_rows(max_m: int) -> None:
+    """bf16 batched linears up to max_m rows on the register-streaming mma.sync kernel (default 8; 0: tcgen05 only)."""
+    lib().mc_sm100_debug_set_mma_rows(max_m)
 
 
 def debug_set_chain(on: bool) -> None:

@@ -8,6 +8,7 @@
 
 #include "fast_dispatch.cuh"
 #include "rows_dispatch.cuh"
+#include "gemm_mma_rows.cuh"
 #include "skinny_gemm.cuh"
 
 namespace mcl {
@@ -369,6 +370,8 @@ void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math) {
 
 int32_t mc_sm100_debug_take_error(void) { return skinny_take_error(); }
 
+void mc_sm100_debug_set_mma_rows(int32_t max_m) { mma_rows_set_max_m(max_m); }
+
 void mc_sm100_hint_next_weights(const void* d_next_w, uint64_t bytes) {
     g_next = (d_next_w != nullptr && aligned16(d_next_w) && bytes >= 16u) ? NextWeights{d_next_w, bytes & ~(uint64_t)15u}
                                                                           : NextWeights{nullptr, 0};
@@ -557,9 +560,9 @@ mc_status_t mc_sm100_gate_up_swiglu(const void* d_w, const float* d_scale, const
         set_error("mc_sm100_gate_up_swiglu: invalid args (M=%u N=%u K=%u)", M, N, K);
         return MC_E_INVALID_ARGUMENT;
     }
+    if (M > 4u && wb == 2) return batched_linear_bf16(d_w, d_x, d_y, M, N, K, true, (cudaStream_t)stream, pdl != 0);
     if (M > 4u)
-        return skinny_gemm(wb == 2 ? SKINNY_W_BF16 : SKINNY_W_E4M3, d_w, d_scale, d_x, nullptr, d_y, M, N, K, true,
-                           (cudaStream_t)stream, pdl != 0);
+        return skinny_gemm(SKINNY_W_E4M3, d_w, d_scale, d_x, nullptr, d_y, M, N, K, true, (cudaStream_t)stream, pdl != 0);
     RowsArgs a{};
     a.w = d_w; a.scale = d_scale; a.x = d_x; a.y = d_y; a.N = N; a.K = K; a.y_stride = N / 2u; a.kseg = K;
     return rows(wb, (int)M, PRO_NONE, EPI_SWIGLU, a, 1, (cudaStream_t)stream, pdl != 0);
@@ -653,8 +656,7 @@ mc_status_t mc_sm100_gemm_bf16(void* stream, void* d_workspace, size_t ws_size, 
     (void)ws_size;
     // launched with the programmatic-dependent-launch attribute: the kernel prefetches only
     // weights before griddepcontrol.wait, so this is equivalent to plain stream order
-    return skinny_gemm(SKINNY_W_BF16, d_a, nullptr, (const uint16_t*)d_b, nullptr, (uint16_t*)d_c, M, N, K, false, st,
-                       true);
+    return batched_linear_bf16(d_a, (const uint16_t*)d_b, (uint16_t*)d_c, M, N, K, false, st, true);
 }
 
 mc_status_t mc_sm100_gemm_fp8_q(void* stream, void* d_workspace, size_t ws_size, uint32_t M, uint32_t N,

@@ -274,6 +274,15 @@ static mc_status_t run_step_sharded(mc_sm100_stack* st, const uint16_t* d_x, int
     return MC_OK;
 }
 
+// A bf16 batched linear inside a step: the tcgen05 kernel wherever it takes the shape -- also at the row counts where
+// the public entry point would pick the register-streaming mma.sync kernel (see linear_cols) -- else the public entry
+// point's CUDA-core fallback.
+static mc_status_t stack_gemm_bf16(const void* w, const uint16_t* x, uint16_t* y, uint32_t M, uint32_t N, uint32_t K, cudaStream_t stream) {
+    if (M >= 2u && mcl::skinny_shape_ok(N, K, 2))
+        return mcl::skinny_gemm(mcl::SKINNY_W_BF16, w, nullptr, x, nullptr, y, M, N, K, false, stream, true);
+    return mc_sm100_gemm_bf16((void*)stream, nullptr, 0, M, N, K, w, x, y);
+}
+
 // o_proj of a batched step: its activation is the first `hidden` columns of the [M, pitch] qkv
 // result (the stand-in for attention).  The tensor-core GEMM reads that column block in place
 // through its tensor map; the CUDA-core forms (fewest rows, shapes TMA cannot take) get a packed copy.
@@ -285,6 +294,9 @@ static mc_status_t linear_cols(mc_sm100_stack* st, uint32_t M, uint32_t l, const
     const void* w = sec(st, l, SEC_O);
     const float* sc = fp8 ? (const float*)sec(st, l, SEC_O_SCALE) : nullptr;
     const bool tensor = (fp8 ? M >= 4u : M >= 2u) && mcl::skinny_shape_ok(rows, H, fp8 ? 1 : 2) && (pitch & 7u) == 0u;
+    // (the tcgen05 kernel also at the row counts where the register-streaming mma.sync kernel wins a chain of identical
+    // calls: between tensor-core kernels of two CTAs per SM that one-CTA-per-SM kernel cannot become resident early, and
+    // the M = 8 step was measured at 2.11 ms with it against 1.91 ms)
     if (tensor)
         return mcl::skinny_gemm(fp8 ? mcl::SKINNY_W_E4M3 : mcl::SKINNY_W_BF16, w, sc, src, nullptr, y, M, rows, H, false, stream, true, pitch);
     const cudaError_t e = cudaMemcpy2DAsync(ctx, (size_t)H * 2, src, (size_t)pitch * 2, (size_t)H * 2, M, cudaMemcpyDeviceToDevice, stream);
@@ -325,7 +337,7 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
     };
     auto linear = [&](uint32_t l, uint32_t wsec, uint32_t ssec, const uint16_t* in, uint32_t rows, uint32_t K) {
         return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, l, wsec), (const float*)sec(st, l, ssec), in, part, M, rows, K, sp, 1)
-                   : mc_sm100_gemm_bf16(sp, nullptr, 0, M, rows, K, sec(st, l, wsec), in, part);
+                   : stack_gemm_bf16(sec(st, l, wsec), in, part, M, rows, K, stream);
     };
     // When every linear of the layer runs on the tensor cores, the GEMM itself stores its result into every rank's
     // buffer, as tagged words (two bf16 + the exchange's 32-bit sequence number; no fence, no flag).  The norms read
@@ -407,7 +419,7 @@ static mc_status_t run_step_sharded_batched(mc_sm100_stack* st, const uint16_t* 
                                      (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
     } else {
         rc = fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, 0, SEC_LM_HEAD), (const float*)sec(st, 0, SEC_LM_HEAD_SCALE), h, logits, M, sv.rows, H, sp, 1)
-                 : mc_sm100_gemm_bf16(sp, nullptr, 0, M, sv.rows, H, sec(st, 0, SEC_LM_HEAD), h, logits);
+                 : stack_gemm_bf16(sec(st, 0, SEC_LM_HEAD), h, logits, M, sv.rows, H, stream);
         if (rc != MC_OK) return rc;
         STEP(mc_sm100_argmax_bf16(logits, M, sv.rows, sv.rows, (int32_t)sv.lo, stage, shard_tok, shard_val, sp, 1));
     }
@@ -500,7 +512,7 @@ static mc_status_t run_step_inner(mc_sm100_stack* st, const uint16_t* d_x, uint3
     if (e != cudaSuccess) { set_error("stack step: copy failed: %s", cudaGetErrorString(e)); return MC_E_CUDA; }
     auto linear = [&](uint32_t l, uint32_t wsec, uint32_t ssec, const uint16_t* x, uint16_t* y, uint32_t N, uint32_t K) {
         return fp8 ? mc_sm100_gemv_fp8_rows_m((const uint8_t*)sec(st, l, wsec), (const float*)sec(st, l, ssec), x, y, M, N, K, sp, 1)
-                   : mc_sm100_gemm_bf16(sp, nullptr, 0, M, N, K, sec(st, l, wsec), x, y);
+                   : stack_gemm_bf16(sec(st, l, wsec), x, y, M, N, K, stream);
     };
     const uint16_t* addend = nullptr;
     for (uint32_t l = 0; l < d.layers; ++l) {

@@ -210,6 +210,32 @@ def test_gate_up_swiglu_epilogue_batched(pkg, g, fp8, M, I, K):
     check_close(g.host_u16(dy), ref, abs_floor=4e-3, what=f"gate_up epilogue batched fp8={fp8} M={M} I={I}", rel_max=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K,swiglu", [(12, 1001, 256, False), (7, 2300, 512, False), (3, 2304, 64, False), (16, 2368, 96, False),
+                                          (12, 1000, 256, True), (6, 2296, 512, True)])
+def test_mma_rows_kernel_forms(pkg, g, M, N, K, swiglu):
+    """The register-streaming mma.sync kernel (bf16, weights with at most 16 rows per SM) in the forms the other tests do not
+    reach: two 8-row activation blocks (M > 8, opened up to 16 rows with the A/B hook), 8-row and 16-row weight blocks with a
+    ragged last block, the SwiGLU epilogue, a K of a few steps only."""
+    w = onp.seeded_bf16(400 + N, (N, K), 0.02)
+    x = onp.seeded_bf16(401 + N, (M, K), 1.0 if swiglu else 0.5)
+    pkg.debug_set_mma_rows(16)
+    try:
+        if swiglu:
+            I = N // 2
+            dy = g.empty_u16(M, I)
+            pkg.launch_gate_up_swiglu(interleaved(g, pkg, w, I), None, g.dev(x), dy, M, N, K)
+            g.sync()
+            check_close(g.host_u16(dy), onp.gate_up_swiglu_bf16(w, x), abs_floor=4e-3, what=f"mma rows swiglu M={M} N={N}", rel_max=2e-2)
+        else:
+            dy = g.empty_u16(M, N)
+            ws = torch.empty(4, dtype=torch.uint8, device="cuda")
+            pkg.gemm_bf16(None, ws, 0, M, N, K, g.dev(w), g.dev(x), dy)
+            g.sync()
+            check_close(g.host_u16(dy), onp.linear_bf16(w, x), what=f"mma rows M={M} N={N} K={K}")
+    finally:
+        pkg.debug_set_mma_rows(8)
+
+
 # ---- batched -------------------------------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 16, 32, 64])
 @pytest.mark.parametrize("N,K", [(K_B, I_B), (2048, 6144), (264, 512)])
