@@ -240,10 +240,6 @@ mc_status_t gemm_mma_rows(const void* w, const uint16_t* x, uint16_t* y, uint32_
 static std::atomic<int> g_max_m{8};
 void mma_rows_set_max_m(int max_m) { g_max_m.store(max_m < 0 ? 0 : (max_m > 16 ? 16 : max_m), std::memory_order_relaxed); }
 
-bool batched_linear_bf16_ok(uint32_t M, uint32_t N, uint32_t K, const void* w, const void* x, uint32_t x_pitch) {
-    return ((int)M <= g_max_m.load(std::memory_order_relaxed) && mma_rows_ok(M, N, K, w, x, x_pitch) && mma_rows_plan(N).r == 1u) || skinny_shape_ok(N, K, 2);
-}
-
 mc_status_t batched_linear_bf16(const void* w, const uint16_t* x, uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu,
                                 cudaStream_t stream, bool pdl, uint32_t x_pitch, const PeerOut* out) {
     if ((int)M <= g_max_m.load(std::memory_order_relaxed) && mma_rows_ok(M, N, K, w, x, x_pitch) && mma_rows_plan(N).r == 1u)

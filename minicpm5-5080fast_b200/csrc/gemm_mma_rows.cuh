@@ -25,6 +25,5 @@ mc_status_t gemm_mma_rows(const void* w, const uint16_t* x, uint16_t* y, uint32_
 mc_status_t batched_linear_bf16(const void* w, const uint16_t* x, uint16_t* y, uint32_t M, uint32_t N, uint32_t K, bool swiglu,
                                 cudaStream_t stream, bool pdl, uint32_t x_pitch = 0, const PeerOut* out = nullptr);
 void mma_rows_set_max_m(int max_m);
-bool batched_linear_bf16_ok(uint32_t M, uint32_t N, uint32_t K, const void* w, const void* x, uint32_t x_pitch);
 
 }  // namespace mcl
