@@ -609,6 +609,15 @@ MC_SM100_API void mc_sm100_debug_set_prefetch(int32_t mode, int32_t chunk_bytes,
  * others on the tcgen05 kernel. */
 MC_SM100_API void mc_sm100_debug_set_mma_rows(int32_t max_m);
 
+/* Host-only views of two launch plans, for tests of the host logic (no CUDA call).  mma_rows_plan: how the
+ * register-streaming GEMM cuts a weight of N rows on a device with `sms` SMs (0 = 148): block height (16 or 8 rows),
+ * blocks a CTA holds at a time, rows the fullest SM walks through.  chain_plan: ring slot size of the persistent M = 1
+ * kernel for a stack of these dimensions (0 = does not fit: per-linear kernels) and rows per slot for the K = hidden
+ * linears, the gate_up pairs and the down projection. */
+MC_SM100_API void mc_sm100_debug_mma_rows_plan(uint32_t N, uint32_t sms, uint32_t* rows, uint32_t* blocks_at_a_time, uint32_t* worst_rows);
+MC_SM100_API void mc_sm100_debug_chain_plan(int32_t fp8, uint32_t hidden, uint32_t inter, uint32_t* slot_bytes, uint32_t* rows_hidden,
+                                            uint32_t* rows_gate_up, uint32_t* rows_down);
+
 /* Host-only self-test of the per-device bookkeeping behind the kernels' shared-memory opt-in (one entry per
  * device, raised once per device and size, safe under racing host threads); makes no CUDA call.  0 = passed. */
 MC_SM100_API int32_t mc_sm100_debug_optin_selftest(void);

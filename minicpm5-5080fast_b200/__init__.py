@@ -117,6 +117,8 @@ SIGNATURES = {
     "mc_sm100_debug_set_chain": (None, [_i32]),
     "mc_sm100_debug_optin_selftest": (_i32, []),
     "mc_sm100_debug_set_mma_rows": (None, [_i32]),
+    "mc_sm100_debug_mma_rows_plan": (None, [_u32, _u32, _vp, _vp, _vp]),
+    "mc_sm100_debug_chain_plan": (None, [_i32, _u32, _u32, _vp, _vp, _vp, _vp]),
     "mc_sm100_debug_set_math": (None, [_i32, _i32]),
     "mc_sm100_debug_take_error": (_i32, []),
 }
@@ -330,6 +332,20 @@ def hint_next_weights(w, nbytes=None):
         lib().mc_sm100_hint_next_weights(None, 0)
     else:
         lib().mc_sm100_hint_next_weights(_p(w), int(nbytes if nbytes is not None else w.numel() * w.element_size()))
+
+
+def debug_mma_rows_plan(n: int, sms: int = 148):
+    """(block rows, blocks a CTA holds at a time, rows the fullest SM walks through) -- host logic only."""
+    a, b, c = _u32(0), _u32(0), _u32(0)
+    lib().mc_sm100_debug_mma_rows_plan(n, sms, C.byref(a), C.byref(b), C.byref(c))
+    return a.value, b.value, c.value
+
+
+def debug_chain_plan(fp8: bool, hidden: int, inter: int):
+    """(slot bytes, rows per slot for K = hidden, for the gate_up pairs, for down) of the persistent M = 1 kernel -- host logic only."""
+    v = [_u32(0) for _ in range(4)]
+    lib().mc_sm100_debug_chain_plan(1 if fp8 else 0, hidden, inter, *[C.byref(x) for x in v])
+    return tuple(x.value for x in v)
 
 
 def debug_set_mma_rows(max_m: int) -> None:

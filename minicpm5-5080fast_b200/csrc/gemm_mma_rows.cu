@@ -182,8 +182,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mma_rows_kernel(const MmaRow
 
 // Block height (16 or 8 rows) and blocks a CTA holds at a time (R): the height that leaves the fullest SM with fewer
 // rows (16 on a tie); R = the most blocks any CTA owns, at most 16.
-MmaRowsPlan mma_rows_plan(uint32_t N) {
-    const uint32_t sms = (uint32_t)sm_count();
+MmaRowsPlan mma_rows_plan(uint32_t N) { return mma_rows_plan(N, (uint32_t)sm_count()); }
+
+MmaRowsPlan mma_rows_plan(uint32_t N, uint32_t sms) {
     MmaRowsPlan best{};
     for (uint32_t rows : {16u, 8u}) {
         const uint32_t blocks = (N + rows - 1u) / rows, grid = blocks < sms ? blocks : sms;

@@ -8,7 +8,8 @@ namespace mcl {
 // How a weight of N rows is cut: blocks of `rows` rows, r of them per CTA at a time; worst_rows = rows the fullest SM
 // walks through, balance = mean rows per SM / worst_rows (1 = perfectly even).
 struct MmaRowsPlan { uint32_t rows, r, blocks, worst_rows; float balance; };
-MmaRowsPlan mma_rows_plan(uint32_t N);
+MmaRowsPlan mma_rows_plan(uint32_t N);                   // for the current device
+MmaRowsPlan mma_rows_plan(uint32_t N, uint32_t sms);     // host logic alone
 
 // Whether the kernel takes this call: bf16 weights, 2 <= M <= 16, K a multiple of 32, 16-byte aligned operands,
 // an activation row pitch that is a multiple of 8 elements.

@@ -8,6 +8,7 @@
 
 #include "fast_dispatch.cuh"
 #include "rows_dispatch.cuh"
+#include "decode_chain.cuh"
 #include "gemm_mma_rows.cuh"
 #include "skinny_gemm.cuh"
 
@@ -371,6 +372,25 @@ void mc_sm100_debug_set_math(int32_t bf16_math, int32_t fp8_math) {
 int32_t mc_sm100_debug_take_error(void) { return skinny_take_error(); }
 
 void mc_sm100_debug_set_mma_rows(int32_t max_m) { mma_rows_set_max_m(max_m); }
+
+// Host-only views of two launch plans (no CUDA call), for tests of the host logic.
+void mc_sm100_debug_mma_rows_plan(uint32_t N, uint32_t sms, uint32_t* rows, uint32_t* blocks_at_a_time, uint32_t* worst_rows) {
+    const MmaRowsPlan p = mma_rows_plan(N, sms == 0u ? 148u : sms);
+    if (rows) *rows = p.rows;
+    if (blocks_at_a_time) *blocks_at_a_time = p.r;
+    if (worst_rows) *worst_rows = p.worst_rows;
+}
+void mc_sm100_debug_chain_plan(int32_t fp8, uint32_t hidden, uint32_t inter, uint32_t* slot_bytes, uint32_t* rows_hidden,
+                               uint32_t* rows_gate_up, uint32_t* rows_down) {
+    const int wb = fp8 ? 1 : 2;
+    const uint32_t kmax = hidden > inter ? hidden : inter;
+    const uint32_t unit_max = (2u * hidden > inter ? 2u * hidden : inter) * (uint32_t)wb;
+    const uint32_t slot = chain_slot_bytes(wb, hidden, kmax, unit_max);
+    if (slot_bytes) *slot_bytes = slot;
+    if (rows_hidden) *rows_hidden = slot ? chain_rows_per_unit(wb, hidden, EPI_STORE, slot) : 0u;
+    if (rows_gate_up) *rows_gate_up = slot ? chain_rows_per_unit(wb, hidden, EPI_SWIGLU, slot) : 0u;
+    if (rows_down) *rows_down = slot ? chain_rows_per_unit(wb, inter, EPI_STORE, slot) : 0u;
+}
 
 void mc_sm100_hint_next_weights(const void* d_next_w, uint64_t bytes) {
     g_next = (d_next_w != nullptr && aligned16(d_next_w) && bytes >= 16u) ? NextWeights{d_next_w, bytes & ~(uint64_t)15u}
