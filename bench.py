@@ -714,8 +714,9 @@ TRAFFIC = {
     ("gemv_fast_kernel", "gate_up", "fp8"): (1.0006, "profiles/gemv_fast_fp8_gate_up_11520x2304.md"),
     ("gemv_fast_kernel", "lm_head", "bf16"): (1.0079, "profiles/gemv_fast_bf16_lm_head_122753x2304.md"),
     ("gemv_fast_kernel", "lm_head", "fp8"): (1.0158, "profiles/gemv_fast_fp8_lm_head_122753x2304.md"),
-    ("skinny_gemm_kernel", "down", "bf16"): (0.9986, "profiles/skinny_gemm_bf16_down_m16_2304x5760.md (M = 16; M = 64: 0.9906)"),
-    ("skinny_gemm_kernel", "down", "fp8"): (1.0006, "profiles/skinny_gemm_fp8_weight_only_down_m8_2304x5760.md (M = 8)"),
+    ("skinny_gemm_kernel", "down", "bf16"): (0.9996, "profiles/skinny_gemm_bf16_down_m16_2304x5760.md (M = 16; M = 64: 0.9916)"),
+    ("skinny_gemm_kernel", "down", "fp8"): (1.0025, "profiles/skinny_gemm_fp8_weight_only_down_m8_2304x5760.md (M = 8)"),
+    ("gemm_mma_rows_kernel", "down", "bf16"): (1.0008, "profiles/gemm_mma_rows_bf16_down_m8_2304x5760.md (M = 8)"),
     ("skinny_gemm_kernel", "down", "fp8_w8a8"): (1.0019, "profiles/skinny_gemm_w8a8_down_m8_2304x5760.md (M = 8; the GEMM launch, its activation already quantised)"),
     ("decode_chain_kernel", "stream", "bf16"): (1.0048, "profiles/decode_chain_persistent_kernel_bf16_fp8_m1.md (4 layers + lm_head captured, scaled by bytes)"),
     # the whole bf16 M = 1 step: byte-weighted mean of its five kernels' ratios
