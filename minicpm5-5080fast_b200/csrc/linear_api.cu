@@ -323,6 +323,74 @@ __global__ void residual_rmsnorm_rows_kernel(uint16_t* __restrict__ res, const u
     if (advance != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *advance = *advance + 1u;
 }
 
+// The same operation for widths that are a multiple of 8 and at most 8192: a thread owns one 16-byte chunk of the row and
+// keeps it in registers, so the row is read once, the norm weights are in flight before the grid dependency resolves,
+// and one barrier separates the loads from the stores.  Element arithmetic as above; only the order of the sum of
+// squares differs.
+__global__ void __launch_bounds__(1024) residual_rmsnorm_rows_vec_kernel(uint16_t* __restrict__ res, const uint16_t* __restrict__ add,
+                                                                         const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
+                                                                         uint32_t n, float eps, const TaggedIn tin, uint32_t* advance) {
+    __shared__ float part[32];
+    const uint32_t c = threadIdx.x;
+    const bool on = c < n / 8u;
+    uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+    if (on) wv = __ldg(reinterpret_cast<const uint4*>(w) + c);
+    pdl_trigger();
+    pdl_wait();
+    uint4* rrow = reinterpret_cast<uint4*>(res + (size_t)blockIdx.x * n);
+    uint32_t r[4] = {0u, 0u, 0u, 0u}, a[4] = {0u, 0u, 0u, 0u};
+    const bool tagged = tin.words != nullptr, adds = tagged || add != nullptr;
+    if (on) {
+        const uint4 rv = rrow[c];
+        r[0] = rv.x; r[1] = rv.y; r[2] = rv.z; r[3] = rv.w;
+        if (tagged) {
+            const uint32_t tag = (*tin.step - 1u) * tin.layers + tin.lsel;
+            const uint64_t* tr = tin.words + (size_t)blockIdx.x * tin.pitch + (size_t)c * 4u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[j] = ld_tagged_pair(tr + j, tag, tin);
+        } else if (add != nullptr) {
+            const uint4 av = reinterpret_cast<const uint4*>(add + (size_t)blockIdx.x * n)[c];
+            a[0] = av.x; a[1] = av.y; a[2] = av.z; a[3] = av.w;
+        }
+    }
+    float f[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float lo = __uint_as_float(r[j] << 16), hi = __uint_as_float(r[j] & 0xFFFF0000u);
+        if (adds) {
+            const uint16_t b0 = f32_to_bf16_bits(lo + __uint_as_float(a[j] << 16));
+            const uint16_t b1 = f32_to_bf16_bits(hi + __uint_as_float(a[j] & 0xFFFF0000u));
+            r[j] = (uint32_t)b0 | ((uint32_t)b1 << 16);
+            lo = __uint_as_float((uint32_t)b0 << 16);
+            hi = __uint_as_float((uint32_t)b1 << 16);
+        }
+        f[2 * j] = lo;
+        f[2 * j + 1] = hi;
+        ss = fmaf(lo, lo, ss);
+        ss = fmaf(hi, hi, ss);
+    }
+    if (on && adds) rrow[c] = make_uint4(r[0], r[1], r[2], r[3]);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0u) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (uint32_t k = 0; k < blockDim.x / 32u; ++k) tot += part[k];
+    const float inv = 1.0f / sqrtf(tot / (float)n + eps);
+    if (on) {
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint16_t o0 = f32_to_bf16_bits(f[2 * j] * inv * __uint_as_float(ww[j] << 16));
+            const uint16_t o1 = f32_to_bf16_bits(f[2 * j + 1] * inv * __uint_as_float(ww[j] & 0xFFFF0000u));
+            o[j] = (uint32_t)o0 | ((uint32_t)o1 << 16);
+        }
+        reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * n)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    if (advance != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *advance = *advance + 1u;
+}
+
 // Tagged gathered buffer -> plain bf16 [rows, cols]: the operand form the tensor-core GEMM's TMA loads need.
 __global__ void detag_rows_kernel(const TaggedIn tin, uint16_t* __restrict__ out, uint32_t cols) {
     pdl_trigger();
@@ -340,7 +408,11 @@ mc_status_t mcl::residual_rmsnorm_rows_tagged(uint16_t* d_res, const uint16_t* d
                                               uint32_t rows, uint32_t n, float eps, const TaggedIn& add, uint32_t* d_advance,
                                               cudaStream_t stream, bool pdl) {
     if (add.words != nullptr && (n & 1u) != 0u) { set_error("residual_rmsnorm_rows: a tagged addend needs an even width"); return MC_E_INVALID_ARGUMENT; }
-    (void)launch(residual_rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, stream, pdl, d_res, d_add, d_norm_w, d_out, n, eps, add, d_advance);
+    const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0u; };
+    const bool vec = (n & 7u) == 0u && n <= 8192u && al16(d_res) && al16(d_norm_w) && al16(d_out) &&
+                     (add.words != nullptr || al16(d_add));
+    if (vec) (void)launch(residual_rmsnorm_rows_vec_kernel, dim3(rows), dim3((n / 8u + 31u) / 32u * 32u), 0, stream, pdl, d_res, d_add, d_norm_w, d_out, n, eps, add, d_advance);
+    else (void)launch(residual_rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, stream, pdl, d_res, d_add, d_norm_w, d_out, n, eps, add, d_advance);
     MCL_CHECK_LAUNCH("residual_rmsnorm_rows");
     return MC_OK;
 }

@@ -457,17 +457,21 @@ def test_gemv_fp8_fast_form_fallbacks(pkg, g, case):
         check_close(got, onp.f32_to_bf16(ref32), abs_floor=1e-4, what=f"fast fp8 {case}")
 
 
-def test_residual_rmsnorm_rows(pkg, g):
-    rows, n = 5, 2304
+# widths: the model's (one 16-byte chunk per thread), one whose last warp is partly idle, the widest the
+# chunk-per-thread kernel takes, and two that fall to the strided kernel (not a multiple of 8; too wide)
+@pytest.mark.parametrize("n", [2304, 40, 8192, 2310, 8200])
+@pytest.mark.parametrize("with_add", [True, False])
+def test_residual_rmsnorm_rows(pkg, g, n, with_add):
+    rows = 5
     res = onp.seeded_bf16(180, (rows, n), 1.2)
     add = onp.seeded_bf16(181, (rows, n), 0.6)
     nw = onp.seeded_bf16(182, (n,), 1.0)
     dres, dout = g.dev(res), g.empty_u16(rows, n)
-    pkg.launch_residual_rmsnorm_rows(dres, g.dev(add), g.dev(nw), dout, rows, n, 1e-6)
+    pkg.launch_residual_rmsnorm_rows(dres, g.dev(add) if with_add else None, g.dev(nw), dout, rows, n, 1e-6)
     g.sync()
-    want_res = onp.add_bf16(res, add)
+    want_res = onp.add_bf16(res, add) if with_add else res
     assert np.array_equal(g.host_u16(dres), want_res)
-    check_close(g.host_u16(dout), onp.rmsnorm_bf16(nw, want_res), what="residual_rmsnorm_rows")
+    check_close(g.host_u16(dout), onp.rmsnorm_bf16(nw, want_res), what=f"residual_rmsnorm_rows n={n}")
 
 
 # ---- peer all-gather kernel on one GPU: self exchange, and the bounded wait running out ---------
